@@ -14,9 +14,10 @@ Beyond it:
   back as soon as every key in it lies before the window of the next token.
 * Mixers that keep a state of fixed size per request get *state slots*: one
   tensor [slots, *shape] per layer; a request takes a slot when it is created
-  (the slot is zeroed) and gives it back when it ends.  The architecture served
-  here has no such mixer; the slots still exist (with no tensors) and carry the
-  per-request slot index.
+  (the slot is zeroed) and gives it back when it ends.  A model without such a
+  mixer still has the slots (with no tensors); they carry the per-request slot index.
+* A mixer that keeps one row per token instead of keys and values per head (a latent from which
+  both are made) gets pages of such rows: [layer in group, 1, page, offset in page, width].
 
 Storage layout of a group: [layer in group, 2 (keys, values), page, kv head,
 offset in page, head size]: the tokens of one page and one head are contiguous.
@@ -31,7 +32,7 @@ import numpy as np
 import torch
 
 from ..config.runtime_config import CacheConfig
-from ..parts.base import PagedKV, RequestState
+from ..parts.base import PagedKV, PagedLatent, RequestState
 
 
 class CacheFullError(RuntimeError):
@@ -79,11 +80,12 @@ class PagePool:
 class CacheGroup:
     """Layers whose mixers need the same kind of pages."""
 
-    need: PagedKV
+    need: PagedKV | PagedLatent
     layers: list[int]
     page_size: int
     pool: PagePool
-    storage: torch.Tensor | None = None           # [len(layers), 2, pages, kv heads, page_size, head size]
+    storage: torch.Tensor | None = None           # [len(layers), 2, pages, kv heads, page_size, head size], or
+                                                  # [len(layers), 1, pages, page_size, width] for latent rows
     layer_slot: dict[int, int] = field(default_factory=dict)
 
 
@@ -143,9 +145,9 @@ class CacheManager:
         self.requests: dict[str, RequestCache] = {}
         self._high_water = {"blocks": 0, "used_tokens": 0, "sequences": 0}
 
-        by_need: dict[PagedKV, CacheGroup] = {}
+        by_need: dict = {}
         for layer, need in enumerate(requirements):
-            if isinstance(need, PagedKV):
+            if isinstance(need, (PagedKV, PagedLatent)):
                 group = by_need.get(need)
                 if group is None:
                     group = CacheGroup(need, [], self.page_size, PagePool(config.num_blocks))
@@ -165,8 +167,11 @@ class CacheManager:
                     self.layer_group[layer] = self.layer_group[source]
                 self.layer_source[layer] = source
         for group in self.groups:
-            shape = (len(group.layers), 2, config.num_blocks, group.need.num_kv_heads, self.page_size,
-                     group.need.head_dim)
+            if isinstance(group.need, PagedLatent):
+                shape = (len(group.layers), 1, config.num_blocks, self.page_size, group.need.width)
+            else:
+                shape = (len(group.layers), 2, config.num_blocks, group.need.num_kv_heads, self.page_size,
+                         group.need.head_dim)
             group.storage = torch.zeros(shape, dtype=dtype, device=self.device)
 
     # -- requests ----------------------------------------------------------------
@@ -283,6 +288,14 @@ class CacheManager:
         for request_id in list(self.requests):
             self.free(request_id)
 
+    def snapshot_states(self) -> dict[int, torch.Tensor]:
+        """Copies of the per-request state tensors (empty for a model without stateful mixers)."""
+        return {layer: tensor.clone() for layer, tensor in self.states.tensors.items()}
+
+    def restore_states(self, saved: dict[int, torch.Tensor]) -> None:
+        for layer, tensor in saved.items():
+            self.states.tensors[layer].copy_(tensor)
+
     # -- metadata of a step -------------------------------------------------------
     def slot_mapping(self, group_index: int, request_id: str, first: int, count: int) -> np.ndarray:
         """Flat cache slot (page * page_size + offset) of positions first .. first+count-1."""
@@ -307,15 +320,17 @@ class CacheManager:
             group_index = self.layer_group[source]
             group = self.groups[group_index]
             storage = group.storage[group.layer_slot[source]]
-            view.keys, view.values, view.group = storage[0], storage[1], group_index
+            view.keys, view.group = storage[0], group_index     # latent rows: [pages, page_size, width], no values
+            view.values = storage[1] if storage.shape[0] > 1 else None
         if source in self.states.tensors:
             view.state = self.states.tensors[source]
         return view
 
     # -- statistics ------------------------------------------------------------
     def bytes_per_page(self, group: CacheGroup) -> int:
-        return (len(group.layers) * 2 * self.page_size * group.need.num_kv_heads * group.need.head_dim
-                * torch.empty((), dtype=self.dtype).element_size())
+        per_token = (group.need.width if isinstance(group.need, PagedLatent)
+                     else 2 * group.need.num_kv_heads * group.need.head_dim)
+        return len(group.layers) * self.page_size * per_token * torch.empty((), dtype=self.dtype).element_size()
 
     def kv_bytes_per_token(self) -> int:
         return sum(self.bytes_per_page(group) // self.page_size for group in self.groups)

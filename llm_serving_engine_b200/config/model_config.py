@@ -42,9 +42,9 @@ class LayerSpec:
     prefix: str
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None      # None (with its norm): a layer without a feed-forward
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: PartSpec | None
     cache_from: int | None = None
 
 
@@ -63,6 +63,8 @@ class ModelSpec:
     lm_head_name: str
     tie_word_embeddings: bool
     max_position_embeddings: int
+    residual_streams: int = 1        # copies of the residual (hyper-connections); read as their sum at the end
+    logit_scale: float = 1.0         # the logits are multiplied by it
 
     def __post_init__(self) -> None:
         for index in self.order:

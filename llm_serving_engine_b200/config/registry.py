@@ -6,6 +6,7 @@ which is kept as the fallback when ``architectures`` is absent.
 """
 from __future__ import annotations
 
+import inspect
 import json
 from dataclasses import dataclass
 from pathlib import Path
@@ -37,6 +38,8 @@ def known_architectures() -> list[str]:
 
 def resolve_architecture(values: dict[str, Any]) -> Architecture:
     names = values.get("architectures") or []
+    if not names and isinstance(values.get("architecture"), str):   # some designs name theirs in one string
+        names = [values["architecture"]]
     if names:
         entry = _ARCHITECTURES.get(names[0])
         if entry is None:
@@ -65,5 +68,24 @@ def load_config(folder_or_dict) -> tuple[Architecture, Any, ModelSpec]:
             raise ConfigError(f"no config.json at {path}")
         values = json.loads(path.read_text())
     entry = resolve_architecture(values)
-    config = entry.config_class.from_dict(values)
+    names = None if isinstance(folder_or_dict, dict) else _checkpoint_tensor_names(Path(folder_or_dict))
+    if names is not None and "tensor_names" in inspect.signature(entry.config_class.from_dict).parameters:
+        config = entry.config_class.from_dict(values, tensor_names=names)   # a design whose file leaves to the tensors what it has
+    else:
+        config = entry.config_class.from_dict(values)
     return entry, config, entry.build_spec(config)
+
+
+def _checkpoint_tensor_names(folder: Path):
+    """Names of the tensors in the safetensors files beside config.json (None when there are none)."""
+    folder = folder if folder.is_dir() else folder.parent
+    files = sorted(folder.glob("*.safetensors"))
+    if not files:
+        return None
+    from safetensors import safe_open
+
+    names: set[str] = set()
+    for filename in files:
+        with safe_open(str(filename), framework="pt", device="cpu") as source:
+            names.update(source.keys())
+    return frozenset(names)

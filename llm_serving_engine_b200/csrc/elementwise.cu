@@ -16,34 +16,43 @@ LSE_CHECK_DEFINE(lse_check_elementwise)
 // residual[t, :] = float(table[ids[t], :])
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab) {
+                                 float* __restrict__ out, int hidden, int vocab, int copies) {
   LSE_TL_BEGIN(1)
   pdl_launch_dependents();
   pdl_wait();
   LSE_TL_MARK(2)
   const int t = blockIdx.x;
   const int id = LSE_CHECKED(ids[t], 0, vocab, -1, LSE_CHECK_TOKEN_ID);
-  float* dst = out + (size_t)t * hidden;
+  float* dst = out + (size_t)t * hidden * copies;   // a row holds `copies` copies of the embedding, side by side
   if (id < 0 || id >= vocab) {  // padding row of a fixed-shape batch
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = 0.f;
+    for (int i = threadIdx.x; i < hidden * copies; i += blockDim.x) dst[i] = 0.f;
     return;
   }
   const T* src = table + (size_t)id * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = to_f32<T>(src[i]);
+    for (int c = 0; c < copies; ++c) dst[(size_t)c * hidden + i] = v;
+  }
   LSE_TL_MARK(3)
+}
+
+extern "C" int lse_embedding_copies(const void* table, int table_dtype, const int* ids, float* out,
+                                    int tokens, int hidden, int vocab, int copies, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (copies <= 0) return LSE_ERR_BAD_ARGUMENT;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == LSE_DTYPE_F32)
+    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, copies);
+  else if (table_dtype == LSE_DTYPE_BF16)
+    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, copies);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
 }
 
 extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out,
                              int tokens, int hidden, int vocab, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
-  const int threads = hidden >= 1024 ? 256 : 128;
-  if (table_dtype == LSE_DTYPE_F32)
-    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
-  else if (table_dtype == LSE_DTYPE_BF16)
-    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
-  else
-    return LSE_ERR_BAD_ARGUMENT;
-  LSE_LAUNCH_CHECK();
+  return lse_embedding_copies(table, table_dtype, ids, out, tokens, hidden, vocab, 1, stream);
 }
 
 // ------------------------------------------------------------------ add + RMSNorm
@@ -571,10 +580,20 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
   LSE_LAUNCH_CHECK();
 }
 
-// ------------------------------------------------------------------ SiLU gate
+// ------------------------------------------------------------------ gated activation (SiLU or tanh-form GELU)
+// ACT 0: silu(g) = g / (1 + exp(-g)).  ACT 1: gelu(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+// FAST: the result is rounded to bfloat16, far more coarsely than the fast exponential and division err.
+template <int ACT, bool FAST>
+__device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 0) return FAST ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + expf(-g));
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+  if (FAST) return g - __fdividef(g, 1.0f + __expf(2.0f * inner));   // 0.5 g (1 + tanh x) = g - g / (1 + exp(2x))
+  return 0.5f * g * (1.0f + tanhf(inner));
+}
+
 // gate_up[t] = [gate (I values) | up (I values)];  out[t, i] = silu(gate_i) * up_i
 // grid: (chunks of the row, tokens); a thread handles 4 consecutive i when I % 4 == 0.
-template <typename TI, typename TO, int VEC>
+template <typename TI, typename TO, int VEC, int ACT>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
                                 TO* __restrict__ out, int inter) {
   LSE_TL_BEGIN(4)
@@ -602,9 +621,8 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
   float y[4];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
-    // a bfloat16 result is rounded far more coarsely than the fast exponential and division err
-    if (sizeof(TO) == 2) y[e] = __fdividef(g[e], 1.0f + __expf(-g[e])) * u[e];
-    else y[e] = (g[e] / (1.0f + expf(-g[e]))) * u[e];
+    if (sizeof(TO) == 2) y[e] = gate_act<ACT, true>(g[e]) * u[e];
+    else y[e] = gate_act<ACT, false>(g[e]) * u[e];
   }
   TO* dst = out + (size_t)t * inter + i;
   if (VEC == 4) store4<TO>(dst, y);
@@ -616,6 +634,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
 // flight per thread (more did not help: the exponentials bound it); the chunks of all rows are
 // numbered flat so that no block is half empty
 constexpr int SILU_UNROLL = 1;
+template <int ACT>
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
                                        int inter, long long total_chunks) {
   LSE_TL_BEGIN(4)
@@ -649,9 +668,8 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
       const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
       const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
       const float ga = __low2float(g2), gb = __high2float(g2);
-      // the result is rounded to bfloat16: the fast exponential and division are far below that
-      __nv_bfloat162 y = __floats2bfloat162_rn(__fdividef(ga, 1.0f + __expf(-ga)) * __low2float(u2),
-                                               __fdividef(gb, 1.0f + __expf(-gb)) * __high2float(u2));
+      __nv_bfloat162 y = __floats2bfloat162_rn(gate_act<ACT, true>(ga) * __low2float(u2),
+                                               gate_act<ACT, true>(gb) * __high2float(u2));
       yw[e] = *reinterpret_cast<uint32_t*>(&y);
     }
     *reinterpret_cast<uint4*>(out + where[k]) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
@@ -659,8 +677,9 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
   LSE_TL_MARK(3)
 }
 
-extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
-                            int out_dtype, int tokens, int inter, cudaStream_t stream) {
+template <int ACT>
+static int gated_act_mul_launch(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
+                                int out_dtype, int tokens, int inter, cudaStream_t stream) {
   if (tokens <= 0 || inter <= 0) return 0;
   if (n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   const bool vec = inter % 4 == 0 && partial_stride % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
@@ -668,16 +687,16 @@ extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, l
   if (vec && inter % 8 == 0 && n_partials == 1 && in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) {
     const long long total_chunks = (long long)tokens * (inter / 8);
     const unsigned blocks = (unsigned)((total_chunks + threads * SILU_UNROLL - 1) / (threads * SILU_UNROLL));
-    lse_launch(silu_mul_bf16x8_kernel, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
+    lse_launch(silu_mul_bf16x8_kernel<ACT>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
                inter, total_chunks);
     LSE_LAUNCH_CHECK();
   }
   const int per_row = vec ? inter / 4 : inter;
   dim3 grid((per_row + threads - 1) / threads, tokens);
 #define LSE_SILU_CASE(TI, TO)                                                                                      \
-  if (vec) lse_launch(silu_mul_kernel<TI, TO, 4>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,         \
+  if (vec) lse_launch(silu_mul_kernel<TI, TO, 4, ACT>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,    \
                       partial_stride, (TO*)out, inter);                                                            \
-  else lse_launch(silu_mul_kernel<TI, TO, 1>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,             \
+  else lse_launch(silu_mul_kernel<TI, TO, 1, ACT>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,        \
                   partial_stride, (TO*)out, inter)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_SILU_CASE(float, float); }
   else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(__nv_bfloat16, __nv_bfloat16); }
@@ -685,6 +704,21 @@ extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, l
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_SILU_CASE
   LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
+                            int out_dtype, int tokens, int inter, cudaStream_t stream) {
+  return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
+}
+
+// activation: 0 = SiLU, 1 = the tanh form of GELU
+extern "C" int lse_gated_act_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
+                                 int out_dtype, int tokens, int inter, int activation, cudaStream_t stream) {
+  if (activation == 0)
+    return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
+  if (activation == 1)
+    return gated_act_mul_launch<1>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
+  return LSE_ERR_BAD_ARGUMENT;
 }
 
 // Switch programmatic dependent launch on (1, the default) or off (0) for every later launch.

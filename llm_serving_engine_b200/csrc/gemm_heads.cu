@@ -1,0 +1,94 @@
+// A product per head: out[t][h][n] = gate[t][h] * sum_k a[t][h][k] * w[h](k, n), the heads' matrices
+// side by side in one tensor.  It is what folds a per-head up-projection into the queries of an attention
+// over a shared latent (w[h] read as [k][n]) and what expands the attended latent into a head's values
+// afterwards (w[h] stored [n][k]): the strides of w say which.  float32 accumulation in k order (one chain
+// per output, so a row's result does not depend on which other rows are in the launch); operands float32
+// or bfloat16, rounded once at the store.  Tiles of 64 x 64 outputs, 16 k at a time, 4 x 4 outputs a thread.
+#include "common.cuh"
+
+namespace {
+constexpr int HG_TILE = 64, HG_K = 16, HG_THREADS = 256;
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(HG_THREADS)
+head_gemm_kernel(const TA* __restrict__ a, long long a_t, long long a_h, const TW* __restrict__ w, long long w_h,
+                 long long w_k, long long w_n, TO* __restrict__ out, long long o_t, long long o_h,
+                 const float* __restrict__ gate, int T, int N, int K) {
+  __shared__ float a_s[HG_K][HG_TILE + 4], w_s[HG_K][HG_TILE + 4];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.z, t0 = blockIdx.y * HG_TILE, n0 = blockIdx.x * HG_TILE;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  const TA* ah = a + (size_t)h * a_h;
+  const TW* wh = w + (size_t)h * w_h;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HG_K) {
+    __syncthreads();
+    for (int e = threadIdx.x; e < HG_K * HG_TILE; e += HG_THREADS) {
+      const int kk = e % HG_K, tt = e / HG_K;     // k fastest: a's rows are contiguous in k
+      const int t = t0 + tt, k = k0 + kk;
+      a_s[kk][tt] = (t < T && k < K) ? to_f32<TA>(ah[(size_t)t * a_t + k]) : 0.f;
+    }
+    for (int e = threadIdx.x; e < HG_K * HG_TILE; e += HG_THREADS) {
+      int kk, nn;
+      if (w_n == 1) { nn = e % HG_TILE; kk = e / HG_TILE; } else { kk = e % HG_K; nn = e / HG_K; }
+      const int n = n0 + nn, k = k0 + kk;
+      w_s[kk][nn] = (n < N && k < K) ? to_f32<TW>(wh[(size_t)k * w_k + (size_t)n * w_n]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HG_K; ++kk) {
+      float av[4], wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { av[i] = a_s[kk][ty * 4 + i]; wv[i] = w_s[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = t0 + ty * 4 + i;
+    if (t >= T) continue;
+    const float g = gate ? gate[(size_t)t * gridDim.z + h] : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) out[(size_t)t * o_t + (size_t)h * o_h + n] = from_f32<TO>(acc[i][j] * g);
+    }
+  }
+}
+}  // namespace
+
+// a: element (t, h, k) at t * a_t + h * a_h + k; w: element (h, k, n) at h * w_h + k * w_k + n * w_n;
+// out: element (t, h, n) at t * o_t + h * o_h + n; gate: float32 [T][heads] or null.
+extern "C" int lse_head_gemm(const void* a, int a_dtype, long long a_t, long long a_h, const void* w, int w_dtype,
+                             long long w_h, long long w_k, long long w_n, void* out, int out_dtype, long long o_t,
+                             long long o_h, const float* gate, int T, int heads, int N, int K, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (heads <= 0 || heads > 65535 || N <= 0 || K <= 0) return LSE_ERR_BAD_ARGUMENT;
+  dim3 grid((N + HG_TILE - 1) / HG_TILE, (T + HG_TILE - 1) / HG_TILE, heads);
+  if (grid.y > 65535) return LSE_ERR_TOO_LARGE;
+#define LSE_HG_CASE(TA, TW, TO)                                                                                 \
+  lse_launch(head_gemm_kernel<TA, TW, TO>, grid, HG_THREADS, 0, stream, (const TA*)a, a_t, a_h, (const TW*)w,    \
+             w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K);
+  typedef __nv_bfloat16 bf;
+  const int code = (a_dtype == LSE_DTYPE_BF16 ? 4 : 0) | (w_dtype == LSE_DTYPE_BF16 ? 2 : 0) | (out_dtype == LSE_DTYPE_BF16 ? 1 : 0);
+  switch (code) {
+    case 0: LSE_HG_CASE(float, float, float) break;
+    case 1: LSE_HG_CASE(float, float, bf) break;
+    case 2: LSE_HG_CASE(float, bf, float) break;
+    case 3: LSE_HG_CASE(float, bf, bf) break;
+    case 4: LSE_HG_CASE(bf, float, float) break;
+    case 5: LSE_HG_CASE(bf, float, bf) break;
+    case 6: LSE_HG_CASE(bf, bf, float) break;
+    default: LSE_HG_CASE(bf, bf, bf) break;
+  }
+#undef LSE_HG_CASE
+  LSE_LAUNCH_CHECK();
+}

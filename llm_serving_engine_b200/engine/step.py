@@ -564,7 +564,11 @@ class StepRunner:
 
         step, caches = self._views(step, slot.device, slot.layout)
         if first_use:
+            # Running the step twice is harmless for pages (the same keys are written again) but not for per-request
+            # states, which a mixer advances by the step's tokens: they are put back after the run ahead of the capture.
+            states = self.cache.snapshot_states()
             self.model.forward(step, caches)
+            self.cache.restore_states(states)
         current = torch.cuda.current_stream()
         current.synchronize()
         if self._capture_stream is None:

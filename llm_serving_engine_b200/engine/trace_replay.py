@@ -26,12 +26,12 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    parser.add_argument("--max-requests", type=int, default=8, help="most requests live at a time")
+    parser.add_argument("--max-requests", type=int, default=4, help="most requests live at a time (state slots)")
     return parser
 
 
 def replay(model_dir, dtype: str, out_dir, max_tokens: int, lines, block_size: int = 16,
-           max_requests: int = 8, report=None) -> None:
+           max_requests: int = 4, report=None) -> None:
     import numpy as np
     import torch
 

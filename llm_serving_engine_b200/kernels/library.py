@@ -14,6 +14,27 @@ _lib = None
 
 _SIGNATURES = {
     "lse_embedding": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_embedding_copies": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_streams_update_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_float, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                                   c_int, c_void_p],
+    "lse_gated_act_mul": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_linear_attention_scan": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p],
+    "lse_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_int,
+                          c_int, c_int, c_float, c_void_p, c_void_p],
+    "lse_latent_prepare": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int,
+                           c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                           c_int, c_int, c_void_p, c_float, c_int, c_int, c_void_p],
+    "lse_latent_query": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_latent_attention_chunk": [],
+    "lse_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int,
+                             c_void_p],
+    "lse_head_gemm": [c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
+                      c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lse_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
                         c_int, c_float, c_int, c_int, c_void_p],
     "lse_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -88,7 +109,8 @@ def register_signatures(signatures: dict) -> None:
             fn.restype = c_int
 
 
-CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc")
+CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc",
+                 "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_attention_latent")
 CHECK_KINDS = {1: "token id", 2: "cache slot", 3: "block-table entry", 4: "segment number", 5: "row index"}
 
 

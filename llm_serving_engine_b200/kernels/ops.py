@@ -45,15 +45,15 @@ def sm_count(device=None) -> int:
     return count
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = float32(table[ids[t]]); ids int32 [T], out float32 [T, H]."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, copies: int = 1) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]), ``copies`` times side by side; ids int32 [T], out float32 [T, copies * H]."""
     _need_cuda(table, ids, out)
     vocab, hidden = table.shape
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
-    assert out.shape == (ids.shape[0], hidden) and out.is_contiguous()
+    assert out.shape == (ids.shape[0], copies * hidden) and out.is_contiguous()
     lib = library.load()
-    check(lib.lse_embedding(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
-                            ids.shape[0], hidden, vocab, _stream()), "embedding")
+    check(lib.lse_embedding_copies(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+                                   ids.shape[0], hidden, vocab, int(copies), _stream()), "embedding")
     return out
 
 
@@ -387,16 +387,20 @@ def attention_tc_status() -> int:
     return int(library.load().lse_attention_tc_status())
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out[t, i] = silu(gate_i) * up_i; ``gate_up`` is [T, 2I] (the row is [gate (I) | up (I)]) or a
-    float32 stack of partial sums [P, T, 2I]."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+    """out[t, i] = act(gate_i) * up_i; ``gate_up`` is [T, 2I] (the row is [gate (I) | up (I)]) or a
+    float32 stack of partial sums [P, T, 2I]; ``activation``: "silu" or "gelu_tanh" (the tanh form of GELU)."""
     _need_cuda(gate_up, out)
     tokens, two_i = gate_up.shape[-2], gate_up.shape[-1]
     assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.is_contiguous()
     gate_up, n_partials, stride = _partials(gate_up, tokens, two_i)
     lib = library.load()
-    check(lib.lse_silu_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
-                           dtype_code(out.dtype), tokens, two_i // 2, _stream()), "silu_mul")
+    check(lib.lse_gated_act_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
+                                dtype_code(out.dtype), tokens, two_i // 2, GATE_ACTIVATIONS[activation], _stream()),
+          "silu_mul")
     return out
 
 
@@ -501,4 +505,187 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
     check(lib.lse_sample(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(),
                          top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(), scratch.data_ptr(),
                          out.data_ptr(), _stream()), "sample")
+    return out
+
+
+# ------------------------------------------------------------------ residual kept in several copies
+def streams_update_rmsnorm(streams: torch.Tensor, n_streams: int, delta: torch.Tensor | None,
+                           scale: torch.Tensor | None, mult: float, mix: torch.Tensor | None,
+                           write_weights: torch.Tensor | None, read_weights: torch.Tensor | None,
+                           weight: torch.Tensor, eps: float, out: torch.Tensor, rows: torch.Tensor | None = None,
+                           write_back: bool = True) -> torch.Tensor:
+    """The pending branch output goes into the copies of the residual, then the next branch's input is read and normed.
+
+    streams float32 [T, S * H] (S copies of width H side by side); delta [T, H], a float32 stack [P, T, H], or None;
+    X'[t] = sum_s mix[s, t] X[s] + write_weights[t] * mult * scale * delta  (mix None: identity; write None: ones;
+    scale float32 [H] or None); u = sum_t read_weights[t] X'[t] (None: ones); out = u / sqrt(mean(u^2) + eps) * weight.
+    ``rows``: int32 row numbers (out has one row each); ``write_back``: store X'."""
+    _need_cuda(streams, delta, scale, mix, write_weights, read_weights, weight, out, rows)
+    tokens = streams.shape[0]
+    hidden = streams.shape[1] // n_streams
+    assert streams.dtype == torch.float32 and streams.is_contiguous() and streams.shape[1] == n_streams * hidden
+    assert weight.dtype == torch.float32 and weight.shape == (hidden,) and out.is_contiguous() and out.shape[1] == hidden
+    for table, count in ((scale, hidden), (mix, n_streams * n_streams), (write_weights, n_streams), (read_weights, n_streams)):
+        assert table is None or (table.dtype == torch.float32 and table.numel() == count and table.is_contiguous())
+    delta, n_partials, stride = _partials(delta, tokens, hidden)
+    n_rows = out.shape[0]
+    assert (rows is None and n_rows == tokens) or (rows is not None and rows.dtype == torch.int32 and rows.shape[0] == n_rows)
+    lib = library.load()
+    delta_code = dtype_code(delta.dtype) if delta is not None else F32
+    check(lib.lse_streams_update_rmsnorm(streams.data_ptr(), _ptr(delta), delta_code, n_partials, stride, _ptr(scale),
+                                         float(mult), _ptr(mix), _ptr(write_weights), _ptr(read_weights),
+                                         weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype), _ptr(rows), n_rows,
+                                         int(n_streams), hidden, float(eps), int(write_back), tokens, _stream()),
+          "streams_update_rmsnorm")
+    return out
+
+
+def _projection(proj: torch.Tensor):
+    """(tensor, dtype code, partial sums, elements between them, elements between rows) of a projection's result:
+    [T, N] in float32 or bfloat16 (rows may be strided) or a float32 stack of partial sums [P, T, N]."""
+    if proj.dim() == 3:
+        assert proj.dtype == torch.float32 and proj.is_contiguous()
+        return proj, F32, proj.shape[0], proj.shape[1] * proj.shape[2], proj.shape[2]
+    assert proj.dim() == 2 and proj.stride(1) == 1
+    return proj, dtype_code(proj.dtype), 1, 0, proj.stride(0)
+
+
+# ------------------------------------------------------------------ linear attention with a decay
+LINEAR_ATTENTION_ACTIVATIONS = {"none": 0, "silu": 1}
+
+
+def linear_attention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor,
+                          state: torch.Tensor, segment_start: torch.Tensor, segment_slot: torch.Tensor,
+                          out: torch.Tensor, heads: int, dim: int, vdim: int, activation: str = "silu") -> torch.Tensor:
+    """S = decay_h S + k v^T, o = S^T q over the rows of every request of the step, in order, from and into
+    ``state`` float32 [slots, heads, dim, vdim].  q, k, v are act(columns of ``proj``) (head h of q at
+    q_off + h * dim and so on); out float32 [T, heads * vdim]."""
+    _need_cuda(proj, decay, state, segment_start, segment_slot, out)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, dim, vdim)
+    assert decay.dtype == torch.float32 and decay.shape == (heads,)
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, heads * vdim)
+    assert segment_start.dtype == torch.int32 and segment_slot.dtype == torch.int32
+    segments = segment_slot.shape[0]
+    assert segment_start.shape[0] == segments + 1
+    lib = library.load()
+    check(lib.lse_linear_attention_scan(proj.data_ptr(), code, n_partials, stride, ld, q_off, k_off, v_off,
+                                        decay.data_ptr(), state.data_ptr(), segment_start.data_ptr(),
+                                        segment_slot.data_ptr(), out.data_ptr(), segments, heads, dim, vdim,
+                                        LINEAR_ATTENTION_ACTIVATIONS[activation], state.shape[0], _stream()),
+          "linear_attention_scan")
+    return out
+
+
+def gated_rmsnorm(values: torch.Tensor, proj: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float,
+                  out: torch.Tensor, segment_of_token: torch.Tensor | None = None) -> torch.Tensor:
+    """out = values / sqrt(mean(values^2) + eps) * weight * sigmoid(gate); values float32 [T, N]; the gate is columns
+    g_off .. g_off + N of ``proj``."""
+    _need_cuda(values, proj, weight, out, segment_of_token)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens, n = values.shape
+    assert values.dtype == torch.float32 and values.is_contiguous() and weight.dtype == torch.float32 and weight.shape == (n,)
+    assert out.shape == (tokens, n) and out.is_contiguous()
+    lib = library.load()
+    check(lib.lse_gated_rmsnorm(values.data_ptr(), proj.data_ptr(), code, n_partials, stride, ld, g_off,
+                                weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens, n, float(eps),
+                                _ptr(segment_of_token), _stream()), "gated_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------------ attention over a cached latent
+def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_mapping: torch.Tensor, eps: float, *,
+                   q_off: int = 0, q_rank: int = 0, q_norm: torch.Tensor | None = None,
+                   q_latent: torch.Tensor | None = None, kv_off: int = -1, rank: int = 0,
+                   kv_norm: torch.Tensor | None = None, rot: int = 0, rot_dims: int = 0,
+                   freq: torch.Tensor | None = None, rot_factor: float = 1.0, cache: torch.Tensor | None = None,
+                   g_off: int = -1, heads: int = 0, gate: torch.Tensor | None = None) -> None:
+    """Per row of the step, from the fused down-projection ``proj``: the normed query latent (columns q_off .. +q_rank,
+    into ``q_latent`` [T, q_rank]); the normed key/value latent (kv_off .. +rank) and the rotated shared key part (the
+    next ``rot`` columns, the first ``rot_dims`` of them rotated) into the token's row of ``cache`` [pages, page_size,
+    rank + rot]; sigmoid of the gate columns (g_off .. +heads) into ``gate`` float32 [T, heads].  Each piece is optional."""
+    _need_cuda(proj, positions, slot_mapping, q_norm, q_latent, kv_norm, freq, cache, gate)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    out_dtype = q_latent.dtype if q_latent is not None else cache.dtype if cache is not None else torch.float32
+    if q_rank:
+        assert q_latent.shape == (tokens, q_rank) and q_latent.is_contiguous() and q_norm.dtype == torch.float32
+    num_slots = 0
+    if kv_off >= 0:
+        assert cache.is_contiguous() and cache.shape[-1] == rank + rot and cache.dtype == out_dtype
+        assert kv_norm.dtype == torch.float32 and kv_norm.shape == (rank,)
+        assert freq.dtype == torch.float64 and freq.shape[0] >= rot_dims // 2
+        num_slots = cache.shape[0] * cache.shape[1]
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.shape == (tokens, heads) and gate.is_contiguous()
+    lib = library.load()
+    check(lib.lse_latent_prepare(proj.data_ptr(), code, n_partials, stride, ld, q_off, q_rank, _ptr(q_norm),
+                                 _ptr(q_latent), kv_off, rank, _ptr(kv_norm), rot, rot_dims, _ptr(freq),
+                                 float(rot_factor), positions.data_ptr(), slot_mapping.data_ptr(), _ptr(cache),
+                                 dtype_code(out_dtype), g_off, heads, _ptr(gate), float(eps), tokens, num_slots,
+                                 _stream()), "latent_prepare")
+
+
+def latent_query(proj: torch.Tensor, q_off: int, heads: int, dim: int, rot: int, rot_dims: int, freq: torch.Tensor,
+                 rot_factor: float, positions: torch.Tensor, segment_of_token: torch.Tensor, q_plain: torch.Tensor,
+                 q_wide: torch.Tensor, at: int) -> None:
+    """Head h's query is columns q_off + h * (dim + rot) .. of ``proj``: its first ``dim`` values go to ``q_plain``
+    [T, heads, dim], its last ``rot`` values, rotated, to ``q_wide`` [T, heads, wide] from column ``at``."""
+    _need_cuda(proj, freq, positions, segment_of_token, q_plain, q_wide)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert q_plain.shape == (tokens, heads, dim) and q_plain.is_contiguous() and q_wide.is_contiguous()
+    assert q_wide.shape[:2] == (tokens, heads) and at + rot <= q_wide.shape[2] and q_wide.dtype == q_plain.dtype
+    assert freq.dtype == torch.float64 and freq.shape[0] >= rot_dims // 2
+    lib = library.load()
+    check(lib.lse_latent_query(proj.data_ptr(), code, n_partials, stride, ld, q_off, heads, dim, rot, rot_dims,
+                               freq.data_ptr(), float(rot_factor), positions.data_ptr(), segment_of_token.data_ptr(),
+                               q_plain.data_ptr(), q_wide.data_ptr(), dtype_code(q_plain.dtype), q_wide.shape[2], at,
+                               tokens, _stream()), "latent_query")
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
+                     segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
+                     sink: torch.Tensor | None = None, window: int = 0, split: bool | None = None) -> torch.Tensor:
+    """Attention of every row of the step over its request's cached latent rows: q [T, heads, DK], cache
+    [pages, page_size, DK], out [T, heads, DV] with DV <= DK: the first DV columns of a row are its value.
+    ``sink`` float32 [heads]: exp(sink_h) joins the softmax's denominator.  ``split`` as for the general kernel."""
+    _need_cuda(q, cache, out, block_tables, segment_of_token, positions, sink)
+    tokens, heads, dk = q.shape
+    dv = out.shape[2]
+    page_size = cache.shape[1]
+    assert q.is_contiguous() and out.is_contiguous() and cache.is_contiguous() and cache.shape[2] == dk
+    assert out.shape[:2] == (tokens, heads) and q.dtype == out.dtype == cache.dtype
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1
+    assert sink is None or (sink.dtype == torch.float32 and sink.shape == (heads,))
+    lib = library.load()
+    partials, max_chunks = None, 0
+    if split if split is not None else tokens <= GENERIC_SPLIT_MAX_ROWS:
+        chunk = int(lib.lse_latent_attention_chunk())
+        max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
+        partials = torch.empty(tokens * heads * max_chunks * (dv + 2), dtype=torch.float32, device=q.device)
+    check(lib.lse_latent_attention(q.data_ptr(), cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
+                                   block_tables.data_ptr(), block_tables.stride(0), segment_of_token.data_ptr(),
+                                   positions.data_ptr(), _ptr(sink), tokens, heads, dk, dv, page_size, float(scale),
+                                   int(window), cache.shape[0], block_tables.shape[0], _ptr(partials), max_chunks,
+                                   _stream()), "latent_attention")
+    return out
+
+
+def head_gemm(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h, n] = gate[t, h] * sum_k a[t, h, k] * weight[h, k, n]: a product per head.  a [T, heads, K] and out
+    [T, heads, N] may be views with strided rows and heads (innermost contiguous); weight [heads, K, N] any strides
+    (pass a transposed view for matrices stored [N, K]); gate float32 [T, heads] or None."""
+    _need_cuda(a, weight, out, gate)
+    tokens, heads, k = a.shape
+    n = out.shape[2]
+    assert weight.shape == (heads, k, n) and out.shape[:2] == (tokens, heads)
+    assert a.stride(2) == 1 and out.stride(2) == 1
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == (tokens, heads) and gate.is_contiguous())
+    lib = library.load()
+    check(lib.lse_head_gemm(a.data_ptr(), dtype_code(a.dtype), a.stride(0), a.stride(1), weight.data_ptr(),
+                            dtype_code(weight.dtype), weight.stride(0), weight.stride(1), weight.stride(2),
+                            out.data_ptr(), dtype_code(out.dtype), out.stride(0), out.stride(1), _ptr(gate), tokens,
+                            heads, n, k, _stream()), "head_gemm")
     return out

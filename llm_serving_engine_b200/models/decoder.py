@@ -22,23 +22,41 @@ def _layer_part_prefixes(layer: LayerSpec) -> dict[str, str]:
     return {role: layer.prefix + names.get(role, role + ".") for role in _PART_ROLES}
 
 
-def _layer_parts(layer: LayerSpec) -> list[tuple[str, type, PartSpec]]:
+def _layer_parts(layer: LayerSpec) -> list[tuple[str, type, PartSpec] | None]:
+    """(tensor prefix, class, description) of the four parts of a layer, in the order a block is built from;
+    None for the feed-forward and its norm of a layer that has none."""
     prefixes = _layer_part_prefixes(layer)
-    return [
+    found = [
         (prefixes["mixer_norm"], NORMS.get(layer.mixer_norm.kind), layer.mixer_norm),
         (prefixes["mixer"], MIXERS.get(layer.mixer.kind), layer.mixer),
+    ]
+    if layer.feed_forward is None:
+        return found + [None, None]
+    return found + [
         (prefixes["feed_forward_norm"], NORMS.get(layer.feed_forward_norm.kind), layer.feed_forward_norm),
         (prefixes["feed_forward"], FEED_FORWARDS.get(layer.feed_forward.kind), layer.feed_forward),
     ]
+
+
+def _block_tensors(layer: LayerSpec, hidden_size: int) -> dict[str, TensorSpec]:
+    """Tensors of the layer's arrangement itself, by their names after the layer's prefix (none for the blocks
+    that registered before ``Block.expected_tensors`` existed)."""
+    declare = getattr(BLOCKS.get(layer.block.kind), "expected_tensors", None)
+    return declare(layer.block.params, hidden_size) if declare else {}
 
 
 def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
     """Every tensor the model reads from the checkpoint, by its full name."""
     out: dict[str, TensorSpec] = {spec.embedding_name: TensorSpec((spec.vocab_size, spec.hidden_size))}
     for layer in spec.layers:
-        for prefix, cls, part in _layer_parts(layer):
+        for entry in _layer_parts(layer):
+            if entry is None:
+                continue
+            prefix, cls, part = entry
             for local, tensor in cls.expected_tensors(part.params, spec.hidden_size).items():
                 out[prefix + local] = tensor
+        for local, tensor in _block_tensors(layer, spec.hidden_size).items():
+            out[layer.prefix + local] = tensor
     norm_cls = NORMS.get(spec.final_norm.kind)
     for local, tensor in norm_cls.expected_tensors(spec.final_norm.params, spec.hidden_size).items():
         out[spec.final_norm_prefix + local] = tensor
@@ -83,15 +101,24 @@ class DecoderModel:
         for index, layer in enumerate(spec.layers):
             ctx = BuildContext(dtype, self.device, spec.hidden_size, index, spec.max_position_embeddings)
             built = []
-            for prefix, cls, part in _layer_parts(layer):
+            for entry in _layer_parts(layer):
+                if entry is None:
+                    built.append(None)
+                    continue
+                prefix, cls, part = entry
                 local = {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
                 built.append(cls(part.params, local, ctx))
             block_cls = BLOCKS.get(layer.block.kind)
-            self.blocks.append(block_cls(layer.block.params, *built))
+            own = {local: weights[layer.prefix + local] for local in _block_tensors(layer, spec.hidden_size)}
+            if own:
+                self.blocks.append(block_cls(layer.block.params, *built, weights=own, ctx=ctx))
+            else:
+                self.blocks.append(block_cls(layer.block.params, *built))
         ctx = BuildContext(dtype, self.device, spec.hidden_size, -1, spec.max_position_embeddings)
         prefix = spec.final_norm_prefix
         local = {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, local, ctx)
+        self.layer_hook = None   # for inspection: called as hook(position in the order, stream) after every layer run
 
     @property
     def graph_safe(self) -> bool:
@@ -120,6 +147,8 @@ class DecoderModel:
         for index in self.spec.order:
             block = self.blocks[index]
             for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+                if part is None:
+                    continue
                 for value in vars(part).values():
                     if isinstance(value, torch.Tensor) and value.dim() >= 1 and value.is_floating_point():
                         total += value.numel() * value.element_size()
@@ -129,12 +158,19 @@ class DecoderModel:
         """Run the step's rows through the layers and return float32 logits
         [number of wanted rows, vocab] (an empty tensor when nothing is wanted)."""
         tokens = step.num_tokens
-        residual = torch.empty((tokens, self.spec.hidden_size), dtype=torch.float32, device=self.device)
-        ops.embedding(self.embedding, step.token_ids, residual)
-        stream = ResidualStream(residual)
+        copies = self.spec.residual_streams
+        residual = torch.empty((tokens, copies * self.spec.hidden_size), dtype=torch.float32, device=self.device)
+        ops.embedding(self.embedding, step.token_ids, residual, copies)   # every copy starts as the embedding
+        stream = ResidualStream(residual, copies=copies)
         for position, index in enumerate(self.spec.order):   # caches run along the order
             self.blocks[index].forward(stream, step, caches[position])
+            if self.layer_hook is not None:
+                self.layer_hook(position, stream)
         if step.num_wanted == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        stream.read = None     # the head reads the sum of the copies
         x = self.final_norm.forward(stream, rows=step.want_rows)
-        return linear(x, self.lm_head, out_dtype=torch.float32)
+        logits = linear(x, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0:
+            logits.mul_(self.spec.logit_scale)
+        return logits

@@ -51,6 +51,16 @@ class PagedKV:
 
 
 @dataclass(frozen=True)
+class PagedLatent:
+    """The mixer keeps one row of ``width`` values per token in pages (a latent from which keys and
+    values of all heads are made, and whatever else of a key is shared by the heads).  ``window`` as
+    for ``PagedKV``."""
+
+    width: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
 class RequestState:
     """The mixer keeps a state of fixed size per request: a tensor of ``shape``
     and ``dtype`` ("float32" or "bfloat16"), zeroed when the request is created."""
@@ -61,13 +71,33 @@ class RequestState:
 
 class ResidualStream:
     """The hidden state between parts: the float32 residual [T, H] and the output
-    of the last branch, not yet added (the next norm adds it in float32)."""
+    of the last branch, not yet added (the next norm adds it in float32).
 
-    __slots__ = ("residual", "delta")
+    A model may keep the residual in ``copies`` copies side by side ([T, copies * H]) and scale what a
+    branch adds: ``delta_mult`` (a constant) and ``delta_scale`` (float32 [H], or None) multiply the
+    pending output; ``mix`` (float32 [copies, copies], indexed [from, to], or None for the identity) and
+    ``write`` (float32 [copies], or None for ones) say how the copies are mixed and how much of the
+    output each receives when it is added; ``read`` (float32 [copies], or None for ones) are the
+    weights with which the next branch reads the copies.  The norm that adds the pending output
+    applies all of it (``Norm.forward``)."""
 
-    def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None) -> None:
+    __slots__ = ("residual", "delta", "copies", "delta_mult", "delta_scale", "mix", "write", "read")
+
+    def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None, copies: int = 1) -> None:
         self.residual = residual
         self.delta = delta
+        self.copies = copies
+        self.delta_mult = 1.0
+        self.delta_scale = None
+        self.mix = None
+        self.write = None
+        self.read = None
+
+    @property
+    def plain(self) -> bool:
+        """One copy, and the pending output is added as it is."""
+        return (self.copies == 1 and self.delta_mult == 1.0 and self.delta_scale is None and self.mix is None
+                and self.write is None and self.read is None)
 
 
 class Part:
@@ -120,15 +150,21 @@ class FeedForward(Part):
 class Block:
     graph_safe = False     # as for ``Part``: the arrangement itself launches nothing that depends on the step's contents
 
-    def __init__(self, params, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm,
-                 feed_forward: FeedForward) -> None:
+    def __init__(self, params, mixer_norm: Norm, mixer: Mixer, feed_forward_norm: Norm | None,
+                 feed_forward: FeedForward | None, weights: dict | None = None, ctx: BuildContext | None = None) -> None:
         self.params = params
         self.mixer_norm, self.mixer = mixer_norm, mixer
-        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward   # both None: a layer without one
+
+    @classmethod
+    def expected_tensors(cls, params: dict[str, Any], hidden_size: int) -> dict[str, TensorSpec]:
+        """Tensors of the arrangement itself (scales, mixing weights), by their names after the layer's prefix."""
+        return {}
 
     def parts(self) -> list:
         """Every part this block runs (a mixer's position encoding included)."""
-        found = [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        found = [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+                 if part is not None]
         position = getattr(self.mixer, "position", None)
         if position is not None:
             found.append(position)

@@ -1,6 +1,9 @@
 """The arrangement of the parts in a layer."""
 from __future__ import annotations
 
+import torch
+
+from ..weights.tensor_spec import TensorSpec
 from .base import Block, ResidualStream, register_block
 
 
@@ -17,3 +20,55 @@ class PreNormResidualBlock(Block):
         stream.delta = self.mixer.forward(x, step, cache)
         x = self.feed_forward_norm.forward(stream)
         stream.delta = self.feed_forward.forward(x)
+
+
+@register_block("residual_streams")
+class ResidualStreamsBlock(Block):
+    """Pre-norm residual layer whose residual is kept in ``streams`` copies (hyper-connections) and whose branch
+    outputs are scaled.
+
+    params: ``streams`` (copies of the residual, the model's), ``residual_mult`` (a constant on every branch output),
+    ``layer_scale`` (a learned vector ``ls<q>`` on the output of branch q), ``hyper`` (learned tables ``hc<q>.in``
+    [streams], ``hc<q>.out`` [streams], ``hc<q>.mix`` [streams, streams] of branch q), ``feed_forward`` (false: the
+    layer has the mixer branch only).  For branch q (1: mixer, 2: feed-forward), over the copies x_1 .. x_S:
+        u = sum_s in[s] x_s;  y = branch(norm(u));  x_t <- sum_s mix[s, t] x_s + residual_mult * out[t] * ls * y
+    (without ``hyper``: in, out are ones and mix the identity; S = 1 gives x <- x + residual_mult * ls * y).
+    The update is left pending in the stream; the next norm's kernel applies it together with its own read."""
+
+    graph_safe = True
+
+    def __init__(self, params, mixer_norm, mixer, feed_forward_norm, feed_forward, weights=None, ctx=None) -> None:
+        super().__init__(params, mixer_norm, mixer, feed_forward_norm, feed_forward)
+        weights = weights or {}
+        self.mult = float(params.get("residual_mult", 1.0))
+        self.streams = int(params.get("streams", 1))
+        self.tables = {}
+        for name in self.expected_tensors(params, 0):
+            self.tables[name] = weights[name].to(torch.float32).contiguous()
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        streams = int(params.get("streams", 1))
+        out = {}
+        for branch in (1, 2) if params.get("feed_forward", True) else (1,):
+            if params.get("layer_scale", False):
+                out[f"ls{branch}"] = TensorSpec((hidden_size,), "norm")
+            if params.get("hyper", False):
+                out[f"hc{branch}.in"] = TensorSpec((streams,), "norm")
+                out[f"hc{branch}.out"] = TensorSpec((streams,), "norm")
+                out[f"hc{branch}.mix"] = TensorSpec((streams, streams), "mixing")
+        return out
+
+    def _branch(self, stream: ResidualStream, number: int, norm, run) -> None:
+        stream.read = self.tables.get(f"hc{number}.in")
+        x = norm.forward(stream)           # applies what the branch before left pending, then reads
+        stream.delta = run(x)
+        stream.delta_mult = self.mult
+        stream.delta_scale = self.tables.get(f"ls{number}")
+        stream.mix = self.tables.get(f"hc{number}.mix")
+        stream.write = self.tables.get(f"hc{number}.out")
+
+    def forward(self, stream: ResidualStream, step, cache) -> None:
+        self._branch(stream, 1, self.mixer_norm, lambda x: self.mixer.forward(x, step, cache))
+        if self.feed_forward is not None:
+            self._branch(stream, 2, self.feed_forward_norm, self.feed_forward.forward)

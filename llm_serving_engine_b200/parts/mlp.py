@@ -1,4 +1,4 @@
-"""Dense SiLU-gated feed-forward (reference ``src/llmserve/model.py:180-188``)."""
+"""Dense gated feed-forward (SiLU-gated in the reference, ``src/llmserve/model.py:180-188``)."""
 from __future__ import annotations
 
 import torch
@@ -9,31 +9,44 @@ from .base import FeedForward, register_feed_forward
 from .linear import linear_partials
 
 
+_DEFAULT_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
+
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
-    """params: ``intermediate_size``.  y = down(silu(gate(x)) * up(x)), no biases; gate and up are stacked
-    into one matrix when the part is built (gate rows, then up rows), and the SiLU kernel adds up the
-    partial sums of their product on the way."""
+    """params: ``intermediate_size``; ``activation`` ("silu", the default, or "gelu_tanh"); ``tensor_names``
+    (the names of the gate, up and down matrices after the part's prefix; default the Qwen2 names).
+    y = down(act(gate(x)) * up(x)), no biases; gate and up are stacked into one matrix when the part is
+    built (gate rows, then up rows), and the activation kernel adds up the partial sums of their product
+    on the way."""
 
     graph_safe = True
 
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         self.inter = int(params["intermediate_size"])
-        self.gate_up_weight = torch.cat([weights["gate_proj.weight"], weights["up_proj.weight"]], dim=0).contiguous()
-        self.down_weight = weights["down_proj.weight"].contiguous()
+        self.activation = params.get("activation", "silu")
+        if self.activation not in ops.GATE_ACTIVATIONS:
+            raise ops.KernelError(f"feed-forward: activation {self.activation!r} is not one of {sorted(ops.GATE_ACTIVATIONS)}")
+        names = {**_DEFAULT_NAMES, **params.get("tensor_names", {})}
+        self.gate_up_weight = torch.cat([weights[names["gate"]], weights[names["up"]]], dim=0).contiguous()
+        self.down_weight = weights[names["down"]].contiguous()
 
     @classmethod
     def expected_tensors(cls, params, hidden_size):
         inter = int(params["intermediate_size"])
+        names = {**_DEFAULT_NAMES, **params.get("tensor_names", {})}
         return {
-            "gate_proj.weight": TensorSpec((inter, hidden_size)),
-            "up_proj.weight": TensorSpec((inter, hidden_size)),
-            "down_proj.weight": TensorSpec((hidden_size, inter)),
+            names["gate"]: TensorSpec((inter, hidden_size)),
+            names["up"]: TensorSpec((inter, hidden_size)),
+            names["down"]: TensorSpec((hidden_size, inter)),
         }
 
     def forward(self, x):
         gate_up = linear_partials(x, self.gate_up_weight)
         act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gate_up, act)
+        ops.silu_mul(gate_up, act, self.activation)
         return linear_partials(act, self.down_weight)
+
+
+register_feed_forward("gated_mlp", SwiGLU)   # the same part under the name that does not say which activation

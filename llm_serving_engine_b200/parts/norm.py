@@ -10,25 +10,39 @@ from .base import Norm, ResidualStream, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """params: ``eps``.  y = (x * rsqrt(mean(x^2) + eps)) * weight, where x is the
-    float32 residual after the pending branch output has been added to it."""
+    """params: ``eps``; ``offset`` (default 0): the stored weight is an offset from this number, y = x_hat *
+    (offset + w); ``weight_name`` (default "weight"): the tensor's name after the part's prefix.
+
+    y = (x * rsqrt(mean(x^2) + eps)) * weight, where x is the float32 residual after the pending branch output has
+    been added to it.  When the stream keeps several copies of the residual, or scales what a branch adds
+    (``ResidualStream``), the same kernel launch mixes the copies, adds the scaled output and reads x as the
+    weighted sum of the copies."""
 
     graph_safe = True
 
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         self.eps = float(params["eps"])
-        self.weight = weights["weight"].to(torch.float32).contiguous()
+        offset = float(params.get("offset", 0.0))
+        weight = weights[params.get("weight_name", "weight")].to(torch.float32)
+        self.weight = (weight + offset if offset else weight).contiguous()
 
     @classmethod
     def expected_tensors(cls, params, hidden_size):
-        return {"weight": TensorSpec((hidden_size,), "norm")}
+        kind = "bias" if float(params.get("offset", 0.0)) else "norm"   # an offset weight is drawn around zero
+        return {params.get("weight_name", "weight"): TensorSpec((hidden_size,), kind)}
 
     def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None) -> torch.Tensor:
+        hidden = self.weight.shape[0]
         n_rows = stream.residual.shape[0] if rows is None else rows.shape[0]
-        out = torch.empty((n_rows, stream.residual.shape[1]), dtype=self.ctx.dtype, device=stream.residual.device)
-        ops.add_rmsnorm(stream.residual, stream.delta, self.weight, self.eps, out, rows=rows,
-                        write_residual=rows is None)
+        out = torch.empty((n_rows, hidden), dtype=self.ctx.dtype, device=stream.residual.device)
+        if stream.plain:
+            ops.add_rmsnorm(stream.residual, stream.delta, self.weight, self.eps, out, rows=rows,
+                            write_residual=rows is None)
+        else:
+            ops.streams_update_rmsnorm(stream.residual, stream.copies, stream.delta, stream.delta_scale,
+                                       stream.delta_mult, stream.mix, stream.write, stream.read, self.weight,
+                                       self.eps, out, rows=rows, write_back=rows is None)
         if rows is None:
             stream.delta = None
         return out
