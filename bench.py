@@ -557,12 +557,20 @@ def kernel_times(run, repeats: int = 3) -> dict:
     import torch
     from torch.profiler import ProfilerActivity, profile
 
-    run()
-    torch.cuda.synchronize()
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for _ in range(repeats):
-            run()
+    from llm_serving_engine_b200.kernels import library
+
+    # Without programmatic dependent launch for the measurement: a kernel that is launched early spends the tail of
+    # the kernel before it waiting, and the profiler would count that wait as its own time.
+    library.load().lse_set_pdl(0)
+    try:
+        run()
         torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(repeats):
+                run()
+            torch.cuda.synchronize()
+    finally:
+        library.load().lse_set_pdl(0 if os.environ.get("LSE_PDL", "1") == "0" else 1)
     table = {}
     for event in prof.key_averages():
         total = getattr(event, "device_time_total", None) or getattr(event, "cuda_time_total", 0)

@@ -393,6 +393,24 @@ extern "C" int lse_latent_query(const void* proj, int in_dtype, int n_partials, 
 
 extern "C" int lse_latent_attention_chunk(void) { return CHUNK; }
 
+// The merge alone: adds up the chunks that a split kernel (this file's, or the tensor-core one) left in `partials`.
+extern "C" int lse_latent_attention_merge(const float* partials, void* out, int dtype, const int* segment_of_token,
+                                          const int* positions, const float* sink, int tokens, int n_q, int DV,
+                                          int window, int max_chunks, int num_segments, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (n_q <= 0 || n_q > 65535 || DV <= 0 || max_chunks <= 0) return LSE_ERR_BAD_ARGUMENT;
+  const dim3 grid(tokens, n_q);
+  const int threads = min(256, ((DV + 31) / 32) * 32);
+  if (dtype == LSE_DTYPE_F32)
+    lse_launch(latent_attention_merge_kernel<float>, grid, threads, 0, stream, partials, (float*)out, segment_of_token,
+               positions, sink, n_q, DV, window, max_chunks, num_segments);
+  else if (dtype == LSE_DTYPE_BF16)
+    lse_launch(latent_attention_merge_kernel<__nv_bfloat16>, grid, threads, 0, stream, partials, (__nv_bfloat16*)out,
+               segment_of_token, positions, sink, n_q, DV, window, max_chunks, num_segments);
+  else return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
+}
+
 // partials != null: a block per chunk of a row, merged by a second kernel (few rows); partials holds
 // tokens * n_q * max_chunks * (DV + 2) floats.
 extern "C" int lse_latent_attention(const void* q, const void* cache, void* out, int dtype, const int* block_tables,

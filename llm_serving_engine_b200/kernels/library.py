@@ -33,6 +33,11 @@ _SIGNATURES = {
     "lse_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_int,
                              c_void_p],
+    "lse_latent_attention_merge": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_void_p],
+    "lse_latent_attention_mma_supported": [c_int, c_int],
+    "lse_latent_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
     "lse_head_gemm": [c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_longlong, c_longlong,
                       c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lse_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -110,7 +115,8 @@ def register_signatures(signatures: dict) -> None:
 
 
 CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc",
-                 "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_attention_latent")
+                 "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_attention_latent",
+                 "lse_check_attention_latent_mma")
 CHECK_KINDS = {1: "token id", 2: "cache slot", 3: "block-table entry", 4: "segment number", 5: "row index"}
 
 

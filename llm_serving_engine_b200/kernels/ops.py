@@ -645,13 +645,26 @@ def latent_query(proj: torch.Tensor, q_off: int, heads: int, dim: int, rot: int,
                                tokens, _stream()), "latent_query")
 
 
+def latent_attention_mma_supported(dk: int, dv: int, dtype: torch.dtype, window: int = 0) -> bool:
+    """Whether the tensor-core kernel takes this shape (bfloat16, DK a multiple of 16, DV a multiple of 8 up to 512,
+    no window); other shapes, and float32, run the general kernel."""
+    if dtype != torch.bfloat16 or window > 0:
+        return False
+    return bool(library.load().lse_latent_attention_mma_supported(int(dk), int(dv)))
+
+
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tables: torch.Tensor,
                      segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
-                     sink: torch.Tensor | None = None, window: int = 0, split: bool | None = None) -> torch.Tensor:
+                     sink: torch.Tensor | None = None, window: int = 0, split: bool | None = None,
+                     segment_start: torch.Tensor | None = None,
+                     segment_first_position: torch.Tensor | None = None, tensor_cores: bool = True) -> torch.Tensor:
     """Attention of every row of the step over its request's cached latent rows: q [T, heads, DK], cache
     [pages, page_size, DK], out [T, heads, DV] with DV <= DK: the first DV columns of a row are its value.
-    ``sink`` float32 [heads]: exp(sink_h) joins the softmax's denominator.  ``split`` as for the general kernel."""
-    _need_cuda(q, cache, out, block_tables, segment_of_token, positions, sink)
+    ``sink`` float32 [heads]: exp(sink_h) joins the softmax's denominator.  ``split``: every chunk of 256 keys of a
+    row gets a block of its own and a second kernel merges them (default: with few rows).  Given the step's
+    ``segment_start`` (int32 [S + 1]) and ``segment_first_position`` (int32 [S]), bfloat16 shapes that the
+    tensor-core kernel takes run there (``tensor_cores=False``: the general kernel, for comparisons)."""
+    _need_cuda(q, cache, out, block_tables, segment_of_token, positions, sink, segment_start, segment_first_position)
     tokens, heads, dk = q.shape
     dv = out.shape[2]
     page_size = cache.shape[1]
@@ -665,6 +678,22 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
         chunk = int(lib.lse_latent_attention_chunk())
         max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
         partials = torch.empty(tokens * heads * max_chunks * (dv + 2), dtype=torch.float32, device=q.device)
+    if (tensor_cores and segment_start is not None and segment_first_position is not None
+            and latent_attention_mma_supported(dk, dv, q.dtype, window)):
+        segments = segment_first_position.shape[0]
+        assert segment_start.dtype == torch.int32 and segment_start.shape[0] == segments + 1
+        assert segments == block_tables.shape[0]
+        check(lib.lse_latent_attention_mma(q.data_ptr(), cache.data_ptr(), out.data_ptr(), block_tables.data_ptr(),
+                                           block_tables.stride(0), segment_start.data_ptr(),
+                                           segment_first_position.data_ptr(), _ptr(sink), tokens, segments, heads, dk,
+                                           dv, page_size, float(scale), cache.shape[0], _ptr(partials), max_chunks,
+                                           _stream()), "latent_attention_mma")
+        if partials is not None:
+            check(lib.lse_latent_attention_merge(partials.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                                                 segment_of_token.data_ptr(), positions.data_ptr(), _ptr(sink), tokens,
+                                                 heads, dv, 0, max_chunks, block_tables.shape[0], _stream()),
+                  "latent_attention_merge")
+        return out
     check(lib.lse_latent_attention(q.data_ptr(), cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
                                    block_tables.data_ptr(), block_tables.stride(0), segment_of_token.data_ptr(),
                                    positions.data_ptr(), _ptr(sink), tokens, heads, dk, dv, page_size, float(scale),

@@ -10,6 +10,8 @@ from ..weights.tensor_spec import TensorSpec
 from .base import Mixer, PagedLatent, register_mixer
 from .linear import linear_partials
 
+PER_HEAD_LIBRARY_ROWS = 32    # above this many bfloat16 rows the per-head products are the library's batched product
+
 _DEFAULT_NAMES = {"q_down": "dq", "q_down_norm": "dq.norm", "q_up": "uq", "q": "q", "kv_down": "dkv",
                   "kv_down_norm": "dkv.norm", "k_up": "uk", "v_up": "uv", "sink": "sink", "gate": "g", "out": "o"}
 
@@ -124,6 +126,19 @@ class LatentAttention(Mixer):
     def cache_requirement(cls, params, hidden_size):
         return PagedLatent(int(params["kv_rank"]) + int(params["rot_dim"]), int(params.get("window", 0)))
 
+    @staticmethod
+    def _per_head(a, weight, out, gate) -> None:
+        """out[t, h] = gate[t, h] * a[t, h] @ weight[h]: many bfloat16 rows go to the library's batched product (the
+        tensor cores), few rows and float32 to the engine's own kernel (true float32, one summation order)."""
+        if a.dtype == torch.bfloat16 and a.shape[0] > PER_HEAD_LIBRARY_ROWS:
+            product = torch.bmm(a.transpose(0, 1), weight)            # [heads, T, N], float32 accumulation
+            if gate is None:
+                out.copy_(product.transpose(0, 1))
+            else:
+                torch.mul(product.transpose(0, 1), gate.unsqueeze(-1), out=out)
+        else:
+            ops.head_gemm(a, weight, out, gate)
+
     def forward(self, x, step, cache):
         tokens, heads = x.shape[0], self.heads
         proj = linear_partials(x, self.in_weight)
@@ -141,10 +156,11 @@ class LatentAttention(Mixer):
         q_wide = torch.empty((tokens, heads, wide), dtype=x.dtype, device=x.device)
         ops.latent_query(queries, 0, heads, self.dim, self.rot_dim, self.rot_dims, self.freq, self.rot_factor,
                          step.positions, step.segment_of_token, q_plain, q_wide, self.rank)
-        ops.head_gemm(q_plain, self.k_up, q_wide[:, :, :self.rank])
+        self._per_head(q_plain, self.k_up, q_wide[:, :, :self.rank], None)
         attended = torch.empty((tokens, heads, self.rank), dtype=x.dtype, device=x.device)
         ops.latent_attention(q_wide, cache.keys, attended, cache.block_tables, step.segment_of_token, step.positions,
-                             self.scale, self.sink, self.window)
+                             self.scale, self.sink, self.window, segment_start=step.segment_start,
+                             segment_first_position=step.segment_first_position)
         values = torch.empty((tokens, heads, self.vdim), dtype=x.dtype, device=x.device)
-        ops.head_gemm(attended, self.v_up, values, gate)
+        self._per_head(attended, self.v_up, values, gate)
         return linear_partials(values.view(tokens, heads * self.vdim), self.out_weight)

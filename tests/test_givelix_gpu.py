@@ -244,6 +244,45 @@ def test_latent_attention_finds_one_far_key_at_every_border(dtype, use_sink):
             assert float((got.float().cpu() - want).abs().max()) <= limit, (special, positions[:3], count)
 
 
+def test_tensor_core_latent_attention_against_the_general_kernel():
+    """Portions of several requests beside single tokens, pages scattered, odd numbers of heads, with and without a
+    sink, whole and split by chunks: the tensor-core kernel against the float32-arithmetic kernel on the same
+    bfloat16 inputs, and one far key that must be found."""
+    from llm_serving_engine_b200.kernels import ops
+
+    torch.manual_seed(8)
+    page = 16
+    for heads, rank, rot in ((3, 64, 16), (16, 128, 32), (40, 192, 16), (6, 24, 8)):
+        width = rank + rot
+        counts, firsts = [70, 1, 33, 1, 5], [300, 519, 0, 0, 63]
+        contexts = [first + count for first, count in zip(firsts, counts)]
+        pages_each = [-(-context // page) for context in contexts]
+        pool = (torch.randn(sum(pages_each) + 3, page, width) * 0.5).to(torch.bfloat16).cuda()
+        order = torch.randperm(sum(pages_each) + 3).to(torch.int32)
+        table = torch.full((len(counts), max(pages_each)), -1, dtype=torch.int32)
+        cursor = 0
+        for index, count in enumerate(pages_each):
+            table[index, :count] = order[cursor:cursor + count]
+            cursor += count
+        total = sum(counts)
+        q = (torch.randn(total, heads, width) * 0.5).to(torch.bfloat16)
+        pool[int(table[0, 1]), 3] = (q[5, heads - 1] * 4.0).cuda()          # key 19 of request 0 stands out for one head
+        starts = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32).cuda()
+        seg = torch.cat([torch.full((count,), index, dtype=torch.int32) for index, count in enumerate(counts)]).cuda()
+        pos = torch.cat([torch.arange(first, first + count, dtype=torch.int32) for first, count in zip(firsts, counts)]).cuda()
+        first_pos = torch.tensor(firsts, dtype=torch.int32).cuda()
+        for sink in (None, torch.linspace(-1.0, 2.0, heads).cuda()):
+            for split in (False, True):
+                want = torch.empty(total, heads, rank, dtype=torch.bfloat16, device="cuda")
+                got = torch.empty_like(want)
+                ops.latent_attention(q.cuda(), pool, want, table.cuda(), seg, pos, 0.3, sink, split=split, tensor_cores=False)
+                ops.latent_attention(q.cuda(), pool, got, table.cuda(), seg, pos, 0.3, sink, split=split,
+                                     segment_start=starts, segment_first_position=first_pos)
+                assert ops.latent_attention_mma_supported(width, rank, torch.bfloat16) == (rank % 8 == 0 and width % 16 == 0)
+                error = float((got.float() - want.float()).abs().max())
+                assert error <= 2e-2 * max(1.0, float(want.float().abs().max())), (heads, rank, rot, sink is not None, split, error)
+
+
 def test_latent_attention_window_edges():
     """The kernel's window parameter: the key just inside the window is seen, the one just outside is not."""
     from llm_serving_engine_b200.kernels import ops
