@@ -420,7 +420,7 @@ extern "C" int lse_latent_attention(const void* q, const void* cache, void* out,
                                     cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (DK <= 0 || DV <= 0 || DV > DK || n_q <= 0 || page_size <= 0) return LSE_ERR_BAD_ARGUMENT;
-  if (DV > 8 * THREADS) return LSE_ERR_TOO_LARGE;
+  if (DV > 4 * THREADS) return LSE_ERR_TOO_LARGE;   // a thread keeps at most four output columns of eight heads
   const size_t smem = latent_smem_bytes(DK);
   if (smem > LATENT_MAX_SMEM) return LSE_ERR_TOO_LARGE;
   const int gchunks = (n_q + GC - 1) / GC;
@@ -453,8 +453,7 @@ extern "C" int lse_latent_attention(const void* q, const void* cache, void* out,
 #define LSE_LAT_DPT(T)                                    \
   if (DV <= THREADS) { LSE_LAT_CASE(T, 1) }               \
   else if (DV <= 2 * THREADS) { LSE_LAT_CASE(T, 2) }      \
-  else if (DV <= 4 * THREADS) { LSE_LAT_CASE(T, 4) }      \
-  else { LSE_LAT_CASE(T, 8) }
+  else { LSE_LAT_CASE(T, 4) }
   if (dtype == LSE_DTYPE_F32) { LSE_LAT_DPT(float) }
   else if (dtype == LSE_DTYPE_BF16) { LSE_LAT_DPT(__nv_bfloat16) }
   else return LSE_ERR_BAD_ARGUMENT;

@@ -63,6 +63,72 @@ head_gemm_kernel(const TA* __restrict__ a, long long a_t, long long a_h, const T
     }
   }
 }
+// Few rows (decoding): a thread owns one output column of one head and streams that column of w once for up to eight
+// rows at a time (the rows' a values wait in shared memory and are read by all threads at once).  The sums run in the
+// same order as above: one chain per output, k ascending, so the two kernels give the same bits.
+constexpr int HF_THREADS = 128, HF_ROWS = 8;
+
+template <typename TW> __device__ __forceinline__ void load_w8(const TW* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load_w8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load_w8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 two = *reinterpret_cast<const __nv_bfloat162*>(&words[i]);
+    v[2 * i] = __low2float(two);
+    v[2 * i + 1] = __high2float(two);
+  }
+}
+
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(HF_THREADS)
+head_gemm_few_kernel(const TA* __restrict__ a, long long a_t, long long a_h, const TW* __restrict__ w, long long w_h,
+                     long long w_k, long long w_n, TO* __restrict__ out, long long o_t, long long o_h,
+                     const float* __restrict__ gate, int T, int N, int K, int vector_k) {
+  extern __shared__ float a_sh[];   // [HF_ROWS][K]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.y, n = blockIdx.x * HF_THREADS + threadIdx.x;
+  const TW* wp = w + (size_t)h * w_h + (size_t)n * w_n;
+  for (int t0 = 0; t0 < T; t0 += HF_ROWS) {
+    const int rows = min(HF_ROWS, T - t0);
+    __syncthreads();
+    for (int e = threadIdx.x; e < HF_ROWS * K; e += HF_THREADS) {
+      const int r = e / K, k = e % K;
+      a_sh[e] = r < rows ? to_f32<TA>(a[(size_t)(t0 + r) * a_t + (size_t)h * a_h + k]) : 0.f;
+    }
+    __syncthreads();
+    if (n >= N) continue;
+    float acc[HF_ROWS];
+#pragma unroll
+    for (int r = 0; r < HF_ROWS; ++r) acc[r] = 0.f;
+    if (vector_k) {          // this column's k values lie side by side: sixteen or thirty-two bytes a load
+      for (int k = 0; k < K; k += 8) {
+        float wv[8];
+        load_w8<TW>(wp + k, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+#pragma unroll
+          for (int r = 0; r < HF_ROWS; ++r) acc[r] = fmaf(a_sh[r * K + k + i], wv[i], acc[r]);
+      }
+    } else {
+#pragma unroll 8
+      for (int k = 0; k < K; ++k) {
+        const float wv = to_f32<TW>(wp[(size_t)k * w_k]);
+#pragma unroll
+        for (int r = 0; r < HF_ROWS; ++r) acc[r] = fmaf(a_sh[r * K + k], wv, acc[r]);
+      }
+    }
+    for (int r = 0; r < rows; ++r) {
+      const float g = gate ? gate[(size_t)(t0 + r) * gridDim.y + h] : 1.f;
+      out[(size_t)(t0 + r) * o_t + (size_t)h * o_h + n] = from_f32<TO>(acc[r] * g);
+    }
+  }
+}
 }  // namespace
 
 // a: element (t, h, k) at t * a_t + h * a_h + k; w: element (h, k, n) at h * w_h + k * w_k + n * w_n;
@@ -74,9 +140,19 @@ extern "C" int lse_head_gemm(const void* a, int a_dtype, long long a_t, long lon
   if (heads <= 0 || heads > 65535 || N <= 0 || K <= 0) return LSE_ERR_BAD_ARGUMENT;
   dim3 grid((N + HG_TILE - 1) / HG_TILE, (T + HG_TILE - 1) / HG_TILE, heads);
   if (grid.y > 65535) return LSE_ERR_TOO_LARGE;
+  const bool few = T <= 32 && (size_t)HF_ROWS * K * sizeof(float) <= 48 * 1024;
+  const dim3 few_grid((N + HF_THREADS - 1) / HF_THREADS, heads);
+  const size_t few_smem = (size_t)HF_ROWS * K * sizeof(float);
+  const size_t w_bytes = w_dtype == LSE_DTYPE_BF16 ? 2 : 4;
+  const int vector_k = (w_k == 1 && K % 8 == 0 && (w_h * w_bytes) % 16 == 0 && (w_n * w_bytes) % 16 == 0 &&
+                        ((uintptr_t)w & 15) == 0) ? 1 : 0;
 #define LSE_HG_CASE(TA, TW, TO)                                                                                 \
-  lse_launch(head_gemm_kernel<TA, TW, TO>, grid, HG_THREADS, 0, stream, (const TA*)a, a_t, a_h, (const TW*)w,    \
-             w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K);
+  if (few)                                                                                                      \
+    lse_launch(head_gemm_few_kernel<TA, TW, TO>, few_grid, HF_THREADS, few_smem, stream, (const TA*)a, a_t, a_h, \
+               (const TW*)w, w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K, vector_k);                        \
+  else                                                                                                          \
+    lse_launch(head_gemm_kernel<TA, TW, TO>, grid, HG_THREADS, 0, stream, (const TA*)a, a_t, a_h, (const TW*)w,  \
+               w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K);
   typedef __nv_bfloat16 bf;
   const int code = (a_dtype == LSE_DTYPE_BF16 ? 4 : 0) | (w_dtype == LSE_DTYPE_BF16 ? 2 : 0) | (out_dtype == LSE_DTYPE_BF16 ? 1 : 0);
   switch (code) {

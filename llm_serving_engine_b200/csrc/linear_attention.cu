@@ -9,7 +9,7 @@
 // thread owns 32 rows of one column of S in registers, so a token costs it 32 updates and a 32-term dot
 // product, and the threads that share a column (dim > 32) add their parts by shuffles.  Columns of S are
 // independent of one another, which is what lets them be spread over blocks.  Tokens are staged in shared
-// memory TT at a time.  Everything is float32: the projections arrive in float32, in bfloat16 or as a
+// memory a few at a time.  Everything is float32: the projections arrive in float32, in bfloat16 or as a
 // stack of float32 partial sums, and are activated in float32.
 #include "common.cuh"
 
@@ -17,7 +17,6 @@ LSE_CHECK_DEFINE(lse_check_linear_attention)
 
 namespace {
 constexpr int LA_THREADS = 128;
-constexpr int LA_TT = 16;        // tokens staged at a time
 constexpr int LA_DPT = 32;       // rows of the state that a thread keeps
 
 template <typename TD>
@@ -30,76 +29,182 @@ __device__ __forceinline__ float la_act(float z, int act) { return act == 1 ? z 
 
 // proj: rows of `ld` values; q of head h at q_off + h * dim, k at k_off + h * dim, v at v_off + h * vdim.
 // PARTS threads share a column (PARTS * 32 >= dim), CW = 32 / PARTS columns a warp, 4 * CW a block.
+//
+// A block's work item is a run of consecutive rows of one request:
+//   chunk_rows == 0: all rows of request blockIdx.x, from and into the request's state slot (few rows, decoding);
+//   chunk_rows  > 0: the rows of every request are cut into chunks of chunk_rows rows, numbered request by request,
+//     and blockIdx.x is a chunk.  phase 1: from a zero state, no outputs, the chunk's own state goes to
+//     chunk_state[chunk].  phase 2: from chunk_state[chunk] (which linear_attention_carry_kernel has turned into the
+//     state at the chunk's start), outputs written, the state is not stored.
+// Chunks are what lets a long prompt use the whole GPU: a request's rows are walked in order only within a chunk.
 template <typename TD, int PARTS>
 __global__ void __launch_bounds__(LA_THREADS)
 linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld,
                              int q_off, int k_off, int v_off, const float* __restrict__ decay,
                              float* __restrict__ state, const int* __restrict__ segment_start,
                              const int* __restrict__ segment_slot, float* __restrict__ out, int heads, int dim,
-                             int vdim, int act, int num_slots) {
+                             int vdim, int act, int num_slots, int num_segments, int chunk_rows, int phase,
+                             float* __restrict__ chunk_state) {
   constexpr int CW = 32 / PARTS;
   constexpr int CB = 4 * CW;
-  constexpr int QS = PARTS * (LA_DPT + 1);          // a token's q (or k) in shared memory: parts padded apart
-  __shared__ float q_s[LA_TT * QS], k_s[LA_TT * QS], v_s[LA_TT * CB];
+  constexpr int PADDED = LA_DPT + 4;                // a part's 32 values, 16-byte aligned and four banks apart from the next part's
+  constexpr int QS = PARTS * PADDED;                // a token's q (or k) in shared memory
+  constexpr int LA_TT = PARTS <= 2 ? 16 : (PARTS == 4 ? 8 : 4);   // tokens staged at a time: eight values of q and of k a thread
+  constexpr int QK_LOADS = LA_TT * PARTS * LA_DPT / LA_THREADS;   // values of q (and of k) a thread stages per tile
+  constexpr int V_LOADS = (LA_TT * CB + LA_THREADS - 1) / LA_THREADS;
+  __shared__ __align__(16) float q_s[LA_TT * QS], k_s[LA_TT * QS], v_s[LA_TT * CB];
+  __shared__ int item[3];
   pdl_launch_dependents();
   pdl_wait();
-  const int seg = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * CB;
-  const int row0 = segment_start[seg], row1 = segment_start[seg + 1];
+  const int h = blockIdx.y, col0 = blockIdx.z * CB;
+  int seg, row0, row1;
+  if (chunk_rows == 0) {
+    seg = blockIdx.x;
+    row0 = segment_start[seg];
+    row1 = segment_start[seg + 1];
+  } else {
+    if (threadIdx.x == 0) {     // which request's which rows chunk blockIdx.x is
+      int before = 0, found = -1, first = 0, last = 0;
+      for (int s = 0; s < num_segments && found < 0; ++s) {
+        const int a = segment_start[s], b = segment_start[s + 1];
+        const int chunks = (b - a + chunk_rows - 1) / chunk_rows;
+        if ((int)blockIdx.x < before + chunks) {
+          found = s;
+          first = a + ((int)blockIdx.x - before) * chunk_rows;
+          last = min(b, first + chunk_rows);
+        }
+        before += chunks;
+      }
+      item[0] = found; item[1] = first; item[2] = last;
+    }
+    __syncthreads();
+    seg = item[0]; row0 = item[1]; row1 = item[2];
+    if (seg < 0) return;
+  }
   if (row1 <= row0) return;
-  const int slot = LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane / CW, cb = warp * CW + lane % CW, col = col0 + cb;
   const float dk = decay[h];
-  float* st = state + ((size_t)slot * heads + h) * dim * vdim;
+  float* st = chunk_rows == 0
+      ? state + ((size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * heads + h) * dim * vdim
+      : chunk_state + ((size_t)blockIdx.x * heads + h) * dim * vdim;
+  const bool from_zero = chunk_rows > 0 && phase == 1;
+  const bool outputs = !(chunk_rows > 0 && phase == 1), store = !(chunk_rows > 0 && phase == 2);
   float s[LA_DPT];
 #pragma unroll
   for (int i = 0; i < LA_DPT; ++i) {
     const int d = part * LA_DPT + i;
-    s[i] = (d < dim && col < vdim) ? st[(size_t)d * vdim + col] : 0.f;
+    s[i] = (!from_zero && d < dim && col < vdim) ? st[(size_t)d * vdim + col] : 0.f;
   }
+  float qv[QK_LOADS], kv[QK_LOADS], vv_in[V_LOADS];
+  auto fetch = [&](int base) {      // a tile's q, k and v into registers, all loads in flight together
+    const int n = min(LA_TT, row1 - base);
+#pragma unroll
+    for (int i = 0; i < QK_LOADS; ++i) {
+      const int e = threadIdx.x + i * LA_THREADS;
+      const int t = e / (PARTS * LA_DPT), d = e % (PARTS * LA_DPT);
+      qv[i] = kv[i] = 0.f;
+      if (t < n && d < dim) {
+        const TD* row = proj + (size_t)(base + t) * ld + h * dim + d;
+        qv[i] = la_load(row + q_off, n_partials, partial_stride);
+        kv[i] = la_load(row + k_off, n_partials, partial_stride);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < V_LOADS; ++i) {
+      const int e = threadIdx.x + i * LA_THREADS;
+      const int t = e / CB, c = e % CB;
+      vv_in[i] = 0.f;
+      if (e < LA_TT * CB && t < n && col0 + c < vdim)
+        vv_in[i] = la_load(proj + (size_t)(base + t) * ld + v_off + h * vdim + col0 + c, n_partials, partial_stride);
+    }
+  };
+  fetch(row0);
   for (int base = row0; base < row1; base += LA_TT) {
     const int n = min(LA_TT, row1 - base);
-    __syncthreads();
-    for (int e = threadIdx.x; e < n * PARTS * LA_DPT; e += LA_THREADS) {
+    __syncthreads();      // the tile before has been used
+#pragma unroll
+    for (int i = 0; i < QK_LOADS; ++i) {
+      const int e = threadIdx.x + i * LA_THREADS;
       const int t = e / (PARTS * LA_DPT), d = e % (PARTS * LA_DPT);
-      float qv = 0.f, kv = 0.f;
-      if (d < dim) {
-        const TD* row = proj + (size_t)(base + t) * ld;
-        qv = la_act(la_load(row + q_off + h * dim + d, n_partials, partial_stride), act);
-        kv = la_act(la_load(row + k_off + h * dim + d, n_partials, partial_stride), act);
-      }
-      const int at = t * QS + (d / LA_DPT) * (LA_DPT + 1) + d % LA_DPT;
-      q_s[at] = qv;
-      k_s[at] = kv;
+      const int at = t * QS + (d / LA_DPT) * PADDED + d % LA_DPT;
+      q_s[at] = la_act(qv[i], act);
+      k_s[at] = la_act(kv[i], act);
     }
-    for (int e = threadIdx.x; e < n * CB; e += LA_THREADS) {
-      const int t = e / CB, c = e % CB;
-      float vv = 0.f;
-      if (col0 + c < vdim)
-        vv = la_act(la_load(proj + (size_t)(base + t) * ld + v_off + h * vdim + col0 + c, n_partials, partial_stride), act);
-      v_s[t * CB + c] = vv;
+#pragma unroll
+    for (int i = 0; i < V_LOADS; ++i) {
+      const int e = threadIdx.x + i * LA_THREADS;
+      if (e < LA_TT * CB) v_s[e] = la_act(vv_in[i], act);
     }
     __syncthreads();
+    if (base + LA_TT < row1) fetch(base + LA_TT);    // the next tile travels while this one is worked on
     for (int t = 0; t < n; ++t) {
-      const float* qr = q_s + t * QS + part * (LA_DPT + 1);
-      const float* kr = k_s + t * QS + part * (LA_DPT + 1);
+      const float4* qr = reinterpret_cast<const float4*>(q_s + t * QS + part * PADDED);
+      const float4* kr = reinterpret_cast<const float4*>(k_s + t * QS + part * PADDED);
       const float vv = v_s[t * CB + cb];
-      float o = 0.f;
+      float o[4] = {0.f, 0.f, 0.f, 0.f};     // four short chains instead of one of 32 dependent additions
 #pragma unroll
-      for (int i = 0; i < LA_DPT; ++i) {
-        s[i] = fmaf(dk, s[i], kr[i] * vv);
-        o = fmaf(s[i], qr[i], o);
+      for (int i = 0; i < LA_DPT / 4; ++i) {
+        const float4 kq = kr[i], qq = qr[i];
+        s[4 * i + 0] = fmaf(dk, s[4 * i + 0], kq.x * vv); o[0] = fmaf(s[4 * i + 0], qq.x, o[0]);
+        s[4 * i + 1] = fmaf(dk, s[4 * i + 1], kq.y * vv); o[1] = fmaf(s[4 * i + 1], qq.y, o[1]);
+        s[4 * i + 2] = fmaf(dk, s[4 * i + 2], kq.z * vv); o[2] = fmaf(s[4 * i + 2], qq.z, o[2]);
+        s[4 * i + 3] = fmaf(dk, s[4 * i + 3], kq.w * vv); o[3] = fmaf(s[4 * i + 3], qq.w, o[3]);
       }
+      if (outputs) {
+        float total = (o[0] + o[1]) + (o[2] + o[3]);
 #pragma unroll
-      for (int off = CW; off < 32; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (part == 0 && col < vdim) out[(size_t)(base + t) * heads * vdim + h * vdim + col] = o;
+        for (int off = CW; off < 32; off <<= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
+        if (part == 0 && col < vdim) out[(size_t)(base + t) * heads * vdim + h * vdim + col] = total;
+      }
     }
   }
+  if (store) {
 #pragma unroll
-  for (int i = 0; i < LA_DPT; ++i) {
-    const int d = part * LA_DPT + i;
-    if (d < dim && col < vdim) st[(size_t)d * vdim + col] = s[i];
+    for (int i = 0; i < LA_DPT; ++i) {
+      const int d = part * LA_DPT + i;
+      if (d < dim && col < vdim) st[(size_t)d * vdim + col] = s[i];
+    }
   }
+}
+
+// Between the two phases: chunk_state[c] holds chunk c's own state (from zero); it becomes the state at the chunk's
+// start, S_start(c + 1) = decay^rows(c) * S_start(c) + own(c), beginning with the request's slot, which receives the
+// state after the request's last chunk.  One thread per element of (request, head, dim, vdim).
+__global__ void __launch_bounds__(256)
+linear_attention_carry_kernel(const float* __restrict__ decay, float* __restrict__ state,
+                              const int* __restrict__ segment_start, const int* __restrict__ segment_slot,
+                              float* __restrict__ chunk_state, int heads, int dim, int vdim, int num_slots,
+                              int chunk_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seg = blockIdx.y;
+  const int a = segment_start[seg], b = segment_start[seg + 1];
+  if (b <= a) return;
+  const size_t per_state = (size_t)heads * dim * vdim;
+  const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_state) return;
+  int before = 0;
+  for (int s = 0; s < seg; ++s) before += (segment_start[s + 1] - segment_start[s] + chunk_rows - 1) / chunk_rows;
+  const int h = (int)(e / ((size_t)dim * vdim));
+  const float dk = decay[h];
+  float full = 1.f;
+  for (int i = 0; i < chunk_rows; ++i) full *= dk;
+  float* slot = state + (size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * per_state + e;
+  float running = *slot;
+  const int chunks = (b - a + chunk_rows - 1) / chunk_rows;
+  for (int c = 0; c < chunks; ++c) {
+    float* own = chunk_state + (size_t)(before + c) * per_state + e;
+    const float mine = *own;
+    *own = running;
+    float power = full;
+    if (c == chunks - 1) {
+      power = 1.f;
+      for (int i = 0; i < b - a - c * chunk_rows; ++i) power *= dk;
+    }
+    running = fmaf(power, running, mine);
+  }
+  *slot = running;
 }
 
 // out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * weight * sigmoid(g[t]); g: columns g_off .. g_off + n of proj.
@@ -125,23 +230,34 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, i
 }
 }  // namespace
 
-// grid: one block row per request of the step (max_segments), empty requests leave at once.
+// chunk_rows == 0: one block row per request of the step (max_segments), empty requests leave at once.
+// chunk_rows > 0: three launches over chunks of chunk_rows rows; chunk_state holds max_chunks states
+// [heads][dim][vdim] (max_chunks >= tokens / chunk_rows + max_segments bounds the number of chunks).
 extern "C" int lse_linear_attention_scan(const void* proj, int proj_dtype, int n_partials, long long partial_stride,
                                          long long ld, int q_off, int k_off, int v_off, const float* decay,
                                          float* state, const int* segment_start, const int* segment_slot, float* out,
                                          int max_segments, int heads, int dim, int vdim, int act, int num_slots,
-                                         cudaStream_t stream) {
+                                         int chunk_rows, float* chunk_state, int max_chunks, cudaStream_t stream) {
   if (max_segments <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || dim > 8 * LA_DPT || heads > 65535) return LSE_ERR_BAD_ARGUMENT;
+  if (chunk_rows < 0 || (chunk_rows > 0 && (chunk_state == nullptr || max_chunks <= 0))) return LSE_ERR_BAD_ARGUMENT;
   int parts = 1;
   while (parts * LA_DPT < dim) parts <<= 1;
 #define LSE_LA_CASE(TD, P)                                                                                       \
   {                                                                                                              \
     const int cb = 4 * (32 / P);                                                                                 \
-    dim3 grid(max_segments, heads, (vdim + cb - 1) / cb);                                                        \
-    lse_launch(linear_attention_scan_kernel<TD, P>, grid, LA_THREADS, 0, stream, (const TD*)proj, n_partials,    \
-               partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start, segment_slot, out, heads,   \
-               dim, vdim, act, num_slots);                                                                       \
+    dim3 grid(chunk_rows ? max_chunks : max_segments, heads, (vdim + cb - 1) / cb);                              \
+    for (int phase = 1; phase <= (chunk_rows ? 2 : 1); ++phase) {                                                \
+      lse_launch(linear_attention_scan_kernel<TD, P>, grid, LA_THREADS, 0, stream, (const TD*)proj, n_partials,  \
+                 partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start, segment_slot, out, heads, \
+                 dim, vdim, act, num_slots, max_segments, chunk_rows, phase, chunk_state);                       \
+      if (chunk_rows && phase == 1) {                                                                            \
+        const size_t per_state = (size_t)heads * dim * vdim;                                                     \
+        lse_launch(linear_attention_carry_kernel, dim3((unsigned)((per_state + 255) / 256), max_segments), 256,  \
+                   0, stream, decay, state, segment_start, segment_slot, chunk_state, heads, dim, vdim,          \
+                   num_slots, chunk_rows);                                                                       \
+      }                                                                                                          \
+    }                                                                                                            \
   }
 #define LSE_LA_PARTS(TD)                                  \
   switch (parts) {                                        \

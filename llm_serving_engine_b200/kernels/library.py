@@ -21,7 +21,7 @@ _SIGNATURES = {
     "lse_gated_act_mul": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lse_linear_attention_scan": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_void_p],
+                                  c_int, c_void_p, c_int, c_void_p],
     "lse_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_int,
                           c_int, c_int, c_float, c_void_p, c_void_p],
     "lse_latent_prepare": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int,

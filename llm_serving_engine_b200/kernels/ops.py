@@ -554,12 +554,20 @@ def _projection(proj: torch.Tensor):
 LINEAR_ATTENTION_ACTIVATIONS = {"none": 0, "silu": 1}
 
 
+LINEAR_ATTENTION_CHUNK = 64          # rows of a chunk when a step's rows are scanned in chunks
+LINEAR_ATTENTION_CHUNKED_FROM = 128  # rows of a step from which they are
+
+
 def linear_attention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: torch.Tensor,
                           state: torch.Tensor, segment_start: torch.Tensor, segment_slot: torch.Tensor,
-                          out: torch.Tensor, heads: int, dim: int, vdim: int, activation: str = "silu") -> torch.Tensor:
+                          out: torch.Tensor, heads: int, dim: int, vdim: int, activation: str = "silu",
+                          chunked: bool | None = None) -> torch.Tensor:
     """S = decay_h S + k v^T, o = S^T q over the rows of every request of the step, in order, from and into
     ``state`` float32 [slots, heads, dim, vdim].  q, k, v are act(columns of ``proj``) (head h of q at
-    q_off + h * dim and so on); out float32 [T, heads * vdim]."""
+    q_off + h * dim and so on); out float32 [T, heads * vdim].  ``chunked`` (default: from
+    ``LINEAR_ATTENTION_CHUNKED_FROM`` rows on): the rows of a request are cut into chunks that are scanned side by
+    side (each chunk's own state from zero, the states carried from chunk to chunk, then the outputs from each
+    chunk's starting state); the result differs from the row-by-row scan by rounding only."""
     _need_cuda(proj, decay, state, segment_start, segment_slot, out)
     proj, code, n_partials, stride, ld = _projection(proj)
     tokens = proj.shape[-2]
@@ -570,10 +578,16 @@ def linear_attention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int
     segments = segment_slot.shape[0]
     assert segment_start.shape[0] == segments + 1
     lib = library.load()
+    chunk_rows, chunk_state, max_chunks = 0, None, 0
+    if chunked if chunked is not None else tokens >= LINEAR_ATTENTION_CHUNKED_FROM:
+        chunk_rows = LINEAR_ATTENTION_CHUNK
+        max_chunks = tokens // chunk_rows + segments
+        chunk_state = torch.empty((max_chunks, heads, dim, vdim), dtype=torch.float32, device=out.device)
     check(lib.lse_linear_attention_scan(proj.data_ptr(), code, n_partials, stride, ld, q_off, k_off, v_off,
                                         decay.data_ptr(), state.data_ptr(), segment_start.data_ptr(),
                                         segment_slot.data_ptr(), out.data_ptr(), segments, heads, dim, vdim,
-                                        LINEAR_ATTENTION_ACTIVATIONS[activation], state.shape[0], _stream()),
+                                        LINEAR_ATTENTION_ACTIVATIONS[activation], state.shape[0], chunk_rows,
+                                        _ptr(chunk_state), max_chunks, _stream()),
           "linear_attention_scan")
     return out
 

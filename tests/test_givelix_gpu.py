@@ -322,7 +322,7 @@ def test_linear_attention_scan_against_the_recurrence():
     torch.manual_seed(5)
     for heads, dim, vdim in ((2, 24, 40), (3, 72, 136), (1, 130, 8)):
         width = heads * (2 * dim + 2 * vdim)
-        counts, slots = [19, 1, 50], [2, 0, 3]
+        counts, slots = [19, 1, 150], [2, 0, 3]
         proj = torch.randn(sum(counts), width)
         decay = torch.tensor([0.3, 0.95, 0.9999][:heads])
         state = torch.randn(4, heads, dim, vdim) * 0.5
@@ -340,15 +340,17 @@ def test_linear_attention_scan_against_the_recurrence():
                     want_state[slot, h] = float(decay[h]) * want_state[slot, h] + torch.outer(k[h], v[h])
                     want[t, h * vdim:(h + 1) * vdim] = want_state[slot, h].t() @ q[h]
             row += count
-        starts = torch.tensor([0, 19, 20, 70, 70], dtype=torch.int32).cuda()       # a fourth, empty request
-        got = torch.empty(sum(counts), heads * vdim, device="cuda")
-        device_state = state.cuda()
-        ops.linear_attention_scan(proj.cuda(), 0, heads * dim, 2 * heads * dim, decay.cuda(), device_state, starts,
-                                  torch.tensor(slots + [1], dtype=torch.int32).cuda(), got, heads, dim, vdim, "silu")
-        scale = float(want.abs().max())
-        assert float((got.cpu() - want).abs().max()) <= 2e-5 * scale
-        assert float((device_state.cpu() - want_state).abs().max()) <= 2e-5 * float(want_state.abs().max())
-        assert torch.equal(device_state[1].cpu(), state[1])                      # the empty request's slot is untouched
+        starts = torch.tensor([0, 19, 20, 170, 170], dtype=torch.int32).cuda()       # a fourth, empty request
+        for chunked in (False, True):      # row by row, and in chunks of 64 rows scanned side by side (19, 1, 64 + 64 + 22)
+            got = torch.empty(sum(counts), heads * vdim, device="cuda")
+            device_state = state.cuda()
+            ops.linear_attention_scan(proj.cuda(), 0, heads * dim, 2 * heads * dim, decay.cuda(), device_state, starts,
+                                      torch.tensor(slots + [1], dtype=torch.int32).cuda(), got, heads, dim, vdim, "silu",
+                                      chunked=chunked)
+            scale = float(want.abs().max())
+            assert float((got.cpu() - want).abs().max()) <= 2e-5 * scale, (heads, dim, vdim, chunked)
+            assert float((device_state.cpu() - want_state).abs().max()) <= 2e-5 * float(want_state.abs().max())
+            assert torch.equal(device_state[1].cpu(), state[1])                  # the empty request's slot is untouched
 
 
 def test_residual_copies_update_and_norm():
