@@ -21,6 +21,7 @@ from pathlib import Path
 
 # Random stand-in models by name: config.json contents of the architecture, sizes only.
 RANDOM_MODELS = {
+    "givelix": dict(vocab_size=260),     # the Givelix design at a small size (``_givelix_stand_in``)
     # the reference's ModelConfig.tiny (src/llmserve/config.py:34-44) over the byte tokenizer's vocabulary
     "tiny": dict(vocab_size=260, hidden_size=128, intermediate_size=352, num_hidden_layers=4, num_attention_heads=4,
                  num_key_value_heads=2, max_position_embeddings=1024, rope_theta=10000.0, rms_norm_eps=1e-6),
@@ -29,8 +30,26 @@ RANDOM_MODELS = {
 }
 
 
+def _givelix_stand_in(vocab_size: int) -> dict:
+    """A small model of the Givelix design: a latent attention layer, a lightning layer, a layer that reads the first
+    layer's cache, a latent attention layer of the second kind, over three residual streams."""
+    rot = {"base": 10000.0, "dims": 8}
+    first = {"heads": 4, "dim": 24, "rot_dim": 8, "vdim": 16, "kv_rank": 48, "q_rank": 64, "scale": 32 ** -0.5, "rot": rot}
+    second = {"heads": 4, "dim": 24, "rot_dim": 8, "vdim": 16, "kv_rank": 48, "scale": 32 ** -0.5,
+              "rot": dict(rot, scaling={"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0})}
+    mlp = {"kind": "dense", "ff": 352}
+    return {"architecture": "Givelix", "vocab": vocab_size, "width": 128, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "streams": 3, "logit_scale": 1.0, "max_position_embeddings": 1024,
+            "layers": [{"type": "latent_attention", "mixer": first, "mlp": mlp},
+                       {"type": "lightning", "mixer": {"heads": 2, "dim": 32, "vdim": 64, "decay": [0.9, 0.995]}, "mlp": None},
+                       {"type": "latent_attention", "mixer": dict(first, kv_from=0), "mlp": mlp},
+                       {"type": "latent_attention_2", "mixer": second, "mlp": mlp}]}
+
+
 def tiny_config(vocab_size: int = 260, name: str = "tiny") -> dict:
     """config.json of a random stand-in model."""
+    if name == "givelix":
+        return _givelix_stand_in(vocab_size)
     return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "attention_bias": True,
             "tie_word_embeddings": True, **RANDOM_MODELS[name], "vocab_size": vocab_size}
 
