@@ -673,28 +673,28 @@ def design_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflop
     g, q = entry["givelix"], entry["qwen2_equal_size"]
     out = {"prefill": {}, "decode": {}}
     # prompt step: per launch of a layer
-    out["prefill"]["givelix latent_attention"] = frac(
-        g["prefill_kernels"], "latent_attention_kernel", 4, tokens * heads * (576 + 512) * 2, 2 * pairs * heads * (576 + 512), fma)
-    out["prefill"]["givelix linear_attention_scan"] = frac(
-        g["prefill_kernels"], "linear_attention_scan", 2, tokens * heads * 128 * 3 * 2 + tokens * heads * 128 * 4,
-        tokens * heads * 128 * 128 * 5, fma)
+    out["prefill"]["givelix latent_attention (tensor cores)"] = frac(
+        g["prefill_kernels"], "latent_attention_mma", 4, tokens * heads * (576 + 512) * 2, 2 * pairs * heads * (576 + 512), tensor)
+    out["prefill"]["givelix linear_attention scan + carry (float32 FMA)"] = frac(
+        g["prefill_kernels"], "linear_attention", 2, tokens * heads * 128 * 3 * 2 + tokens * heads * 128 * 4,
+        tokens * heads * 128 * 128 * 2 * 4, fma)       # two passes of (state update + its use), a multiply-add each
     out["prefill"]["givelix streams_update_rmsnorm"] = frac(
         g["prefill_kernels"], "streams_update_rmsnorm", 11, tokens * width * (4 * 4 * 2 + 2 + 2), 0, fma)
-    out["prefill"]["givelix head_gemm"] = frac(
-        g["prefill_kernels"], "head_gemm", 8, tokens * heads * (128 + 512) * 2, 2 * tokens * heads * 128 * 512, fma)
-    out["prefill"]["qwen2 attention"] = frac(
-        q["prefill_kernels"], "attention", 6, tokens * (heads + 2 * kv_heads) * 128 * 2 * 2, 4 * pairs * heads * 128, tensor)
+    out["prefill"]["qwen2 attention (tcgen05)"] = frac(
+        q["prefill_kernels"], "attn_", 6, tokens * (heads + 2 * kv_heads) * 128 * 2 * 2, 4 * pairs * heads * 128, tensor)
     out["prefill"]["qwen2 add_rmsnorm"] = frac(
         q["prefill_kernels"], "add_rmsnorm", 13, tokens * width * (4 * 2 + 2 + 2), 0, fma)
     # decode step at `batch` requests over 2,048-token contexts
-    out["decode"]["givelix latent_attention"] = frac(
-        g["decode_kernels"], "latent_attention_kernel", 4, batch * tokens * 576 * 2, 2 * batch * tokens * heads * (576 + 512), fma)
-    out["decode"]["givelix linear_attention_scan"] = frac(
-        g["decode_kernels"], "linear_attention_scan", 2, batch * heads * 128 * 128 * 4 * 2, batch * heads * 128 * 128 * 5, fma)
+    out["decode"]["givelix latent_attention (tensor cores, chunks + merge)"] = frac(
+        g["decode_kernels"], "latent_attention_m", 4, batch * tokens * 576 * 2, 2 * batch * tokens * heads * (576 + 512), tensor)
+    out["decode"]["givelix linear_attention scan"] = frac(
+        g["decode_kernels"], "linear_attention", 2, batch * heads * 128 * 128 * 4 * 2, batch * heads * 128 * 128 * 4, fma)
+    out["decode"]["givelix per-head products (few rows)"] = frac(
+        g["decode_kernels"], "head_gemm", 8, heads * 128 * 512 * 2, 2 * batch * heads * 128 * 512, fma)
     out["decode"]["givelix streams_update_rmsnorm"] = frac(
         g["decode_kernels"], "streams_update_rmsnorm", 11, batch * width * (4 * 4 * 2 + 4 + 2), 0, fma)
-    out["decode"]["qwen2 attention"] = frac(
-        q["decode_kernels"], "attention", 6, batch * tokens * 2 * kv_heads * 128 * 2, 4 * batch * tokens * heads * 128, tensor)
+    out["decode"]["qwen2 attention (mma.sync, split keys)"] = frac(
+        q["decode_kernels"], "attn_", 6, batch * tokens * 2 * kv_heads * 128 * 2, 4 * batch * tokens * heads * 128, tensor)
     out["decode"]["qwen2 add_rmsnorm"] = frac(
         q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
     return out

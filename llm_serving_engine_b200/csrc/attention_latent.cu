@@ -21,8 +21,8 @@
 //     denominator that has no key and no value.
 //
 // Rotation: the pair (2i, 2i+1), i < rot_dims / 2, by the angle position * freq[i]; cos and sin times `rot_factor`
-// (frequency scaling schemes are folded into freq and rot_factor by the host).  The angle is formed and reduced in
-// double precision: a float32 product of a position in the thousands and a frequency near one is already off by 1e-4.
+// (frequency scaling schemes are folded into freq and rot_factor by the host).  The angle is formed and brought into [-pi, pi] in
+// double precision, its sine and cosine taken in float32: a float32 product of a position in the thousands and a frequency near one is already off by 1e-4.
 #include "common.cuh"
 
 LSE_CHECK_DEFINE(lse_check_attention_latent)
@@ -36,14 +36,19 @@ __device__ __forceinline__ float lat_load(const TD* p, int n_partials, long long
 }
 
 __device__ __forceinline__ void lat_sincos(int position, double freq, float factor, float& sn, float& cs) {
-  double s, c;
-  sincos((double)position * freq, &s, &c);
-  sn = (float)s * factor;
-  cs = (float)c * factor;
+  double angle = (double)position * freq;
+  angle -= 6.283185307179586 * rint(angle * 0.15915494309189535);    // into [-pi, pi], still in double
+  float s, c;
+  sincosf((float)angle, &s, &c);
+  sn = s * factor;
+  cs = c * factor;
 }
 
 constexpr int PREP_THREADS = 128;
 
+// `width` columns of the row are used (all that the stacked projection has).  staged: the row's partial sums are added
+// once, sixteen bytes and eight partial sums a round trip, into shared memory (width floats), and every later pass
+// reads it there; else (a row too wide for that) every pass adds them up again from global memory.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(PREP_THREADS)
 latent_prepare_kernel(const TI* __restrict__ proj, int n_partials, long long partial_stride, long long ld,
@@ -51,44 +56,60 @@ latent_prepare_kernel(const TI* __restrict__ proj, int n_partials, long long par
                       int kv_off, int rank, const float* __restrict__ kv_norm, int rot, int rot_dims,
                       const double* __restrict__ freq, float rot_factor, const int* __restrict__ positions,
                       const int* __restrict__ slot_mapping, TO* __restrict__ cache, int g_off, int heads,
-                      float* __restrict__ gate, float eps, int num_slots) {
+                      float* __restrict__ gate, float eps, int num_slots, int width, int staged) {
+  extern __shared__ float row_s[];
   __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const TI* row = proj + (size_t)t * ld;
   const int slot = LSE_CHECKED(slot_mapping[t], -1, num_slots, -1, LSE_CHECK_CACHE_SLOT);
+  if (staged) {
+    for (int c = threadIdx.x; c < width; c += PREP_THREADS) {
+      float total = 0.f;
+      for (int p0 = 0; p0 < n_partials; p0 += 8) {
+        float part[8];
+#pragma unroll
+        for (int p = 0; p < 8; ++p) part[p] = p0 + p < n_partials ? to_f32<TI>(row[(size_t)(p0 + p) * partial_stride + c]) : 0.f;
+#pragma unroll
+        for (int p = 0; p < 8; ++p) total += part[p];
+      }
+      row_s[c] = total;
+    }
+    __syncthreads();
+  }
+  auto value = [&](int c) { return staged ? row_s[c] : lat_load(row + c, n_partials, partial_stride); };
   if (q_rank > 0) {
     float sq = 0.f;
     for (int i = threadIdx.x; i < q_rank; i += PREP_THREADS) {
-      const float v = lat_load(row + q_off + i, n_partials, partial_stride);
+      const float v = value(q_off + i);
       sq = fmaf(v, v, sq);
     }
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)q_rank + eps);
     for (int i = threadIdx.x; i < q_rank; i += PREP_THREADS)
-      q_latent[(size_t)t * q_rank + i] = from_f32<TO>((lat_load(row + q_off + i, n_partials, partial_stride) * inv) * q_norm[i]);
+      q_latent[(size_t)t * q_rank + i] = from_f32<TO>((value(q_off + i) * inv) * q_norm[i]);
   }
   if (gate) {
     for (int h = threadIdx.x; h < heads; h += PREP_THREADS)
-      gate[(size_t)t * heads + h] = 1.f / (1.f + expf(-lat_load(row + g_off + h, n_partials, partial_stride)));
+      gate[(size_t)t * heads + h] = 1.f / (1.f + expf(-value(g_off + h)));
   }
   if (kv_off >= 0) {
     float sq = 0.f;
     for (int i = threadIdx.x; i < rank; i += PREP_THREADS) {
-      const float v = lat_load(row + kv_off + i, n_partials, partial_stride);
+      const float v = value(kv_off + i);
       sq = fmaf(v, v, sq);
     }
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)rank + eps);
     if (slot < 0) return;    // a padding row: nothing is cached
     TO* dst = cache + (size_t)slot * (rank + rot);
     for (int i = threadIdx.x; i < rank; i += PREP_THREADS)
-      dst[i] = from_f32<TO>((lat_load(row + kv_off + i, n_partials, partial_stride) * inv) * kv_norm[i]);
+      dst[i] = from_f32<TO>((value(kv_off + i) * inv) * kv_norm[i]);
     const int position = positions[t];
-    const TI* src = row + kv_off + rank;
+    const int src = kv_off + rank;
     for (int i = threadIdx.x; i < rot / 2 + (rot & 1); i += PREP_THREADS) {
-      const float a = lat_load(src + 2 * i, n_partials, partial_stride);
+      const float a = value(src + 2 * i);
       if (2 * i + 1 >= rot) { dst[rank + 2 * i] = from_f32<TO>(a); continue; }
-      const float b = lat_load(src + 2 * i + 1, n_partials, partial_stride);
+      const float b = value(src + 2 * i + 1);
       if (2 * i + 1 < rot_dims) {
         float sn, cs;
         lat_sincos(position, freq[i], rot_factor, sn, cs);
@@ -355,13 +376,17 @@ extern "C" int lse_latent_prepare(const void* proj, int in_dtype, int n_partials
                                   int q_off, int q_rank, const float* q_norm, void* q_latent, int kv_off, int rank,
                                   const float* kv_norm, int rot, int rot_dims, const double* freq, float rot_factor,
                                   const int* positions, const int* slot_mapping, void* cache, int out_dtype, int g_off,
-                                  int heads, float* gate, float eps, int tokens, int num_slots, cudaStream_t stream) {
+                                  int heads, float* gate, float eps, int tokens, int num_slots, int width,
+                                  cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (rot_dims > rot || (rot_dims & 1) || rank < 0) return LSE_ERR_BAD_ARGUMENT;
+  if (rot_dims > rot || (rot_dims & 1) || rank < 0 || width <= 0) return LSE_ERR_BAD_ARGUMENT;
+  // one set of sums (many rows: a prompt's portion) is read where it lies; a stack of partial sums is added up once
+  const int staged = (n_partials > 1 && (size_t)width * sizeof(float) <= 40 * 1024) ? 1 : 0;
+  const size_t smem = staged ? (size_t)width * sizeof(float) : 0;
 #define LSE_PREP_CASE(TI, TO)                                                                                      \
-  lse_launch(latent_prepare_kernel<TI, TO>, tokens, PREP_THREADS, 0, stream, (const TI*)proj, n_partials,         \
+  lse_launch(latent_prepare_kernel<TI, TO>, tokens, PREP_THREADS, smem, stream, (const TI*)proj, n_partials,      \
              partial_stride, ld, q_off, q_rank, q_norm, (TO*)q_latent, kv_off, rank, kv_norm, rot, rot_dims, freq, \
-             rot_factor, positions, slot_mapping, (TO*)cache, g_off, heads, gate, eps, num_slots);
+             rot_factor, positions, slot_mapping, (TO*)cache, g_off, heads, gate, eps, num_slots, width, staged);
   const bool i32 = in_dtype == LSE_DTYPE_F32, o32 = out_dtype == LSE_DTYPE_F32;
   if (i32 && o32) LSE_PREP_CASE(float, float)
   else if (i32 && !o32) LSE_PREP_CASE(float, __nv_bfloat16)

@@ -63,10 +63,15 @@ head_gemm_kernel(const TA* __restrict__ a, long long a_t, long long a_h, const T
     }
   }
 }
-// Few rows (decoding): a thread owns one output column of one head and streams that column of w once for up to eight
-// rows at a time (the rows' a values wait in shared memory and are read by all threads at once).  The sums run in the
-// same order as above: one chain per output, k ascending, so the two kernels give the same bits.
-constexpr int HF_THREADS = 128, HF_ROWS = 8;
+// Few rows (decoding): the matrices are read once, by many warps, with all of a lane's loads in flight together.
+// Up to eight rows at a time wait in shared memory as float32.  Two layouts of w:
+//   * a column's k values lie side by side (w_k == 1): a warp owns four columns, its lanes split k in pieces of
+//     eight (sixteen bytes of bfloat16 a load, a warp reads a column's 512 bytes in one go) and add their parts by
+//     shuffles;
+//   * a k's columns lie side by side (w_n == 1): a lane owns a column, the block's four warps split k, and the
+//     warps' parts are added in warp order through shared memory.
+// The order of the sums differs from the tiled kernel's by rounding only.
+constexpr int HF_THREADS = 128, HF_ROWS = 8, HF_COLS = 4;
 
 template <typename TW> __device__ __forceinline__ void load_w8(const TW* p, float (&v)[8]);
 template <> __device__ __forceinline__ void load_w8<float>(const float* p, float (&v)[8]) {
@@ -84,16 +89,17 @@ template <> __device__ __forceinline__ void load_w8<__nv_bfloat16>(const __nv_bf
   }
 }
 
-template <typename TA, typename TW, typename TO>
+// KSIDE: w_k == 1 and aligned for vector loads (grid.x = N / 16 columns a block); else grid.x = N / 32.
+template <typename TA, typename TW, typename TO, bool KSIDE>
 __global__ void __launch_bounds__(HF_THREADS)
 head_gemm_few_kernel(const TA* __restrict__ a, long long a_t, long long a_h, const TW* __restrict__ w, long long w_h,
                      long long w_k, long long w_n, TO* __restrict__ out, long long o_t, long long o_h,
-                     const float* __restrict__ gate, int T, int N, int K, int vector_k) {
-  extern __shared__ float a_sh[];   // [HF_ROWS][K]
+                     const float* __restrict__ gate, int T, int N, int K) {
+  extern __shared__ __align__(16) float a_sh[];   // [HF_ROWS][K], then (columns side by side) [4][HF_ROWS][32] parts
   pdl_launch_dependents();
   pdl_wait();
-  const int h = blockIdx.y, n = blockIdx.x * HF_THREADS + threadIdx.x;
-  const TW* wp = w + (size_t)h * w_h + (size_t)n * w_n;
+  const int h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const TW* wh = w + (size_t)h * w_h;
   for (int t0 = 0; t0 < T; t0 += HF_ROWS) {
     const int rows = min(HF_ROWS, T - t0);
     __syncthreads();
@@ -102,30 +108,74 @@ head_gemm_few_kernel(const TA* __restrict__ a, long long a_t, long long a_h, con
       a_sh[e] = r < rows ? to_f32<TA>(a[(size_t)(t0 + r) * a_t + (size_t)h * a_h + k]) : 0.f;
     }
     __syncthreads();
-    if (n >= N) continue;
-    float acc[HF_ROWS];
+    if (KSIDE) {
+      const int n0 = (blockIdx.x * 4 + warp) * HF_COLS;
+      float acc[HF_COLS][HF_ROWS];
 #pragma unroll
-    for (int r = 0; r < HF_ROWS; ++r) acc[r] = 0.f;
-    if (vector_k) {          // this column's k values lie side by side: sixteen or thirty-two bytes a load
-      for (int k = 0; k < K; k += 8) {
-        float wv[8];
-        load_w8<TW>(wp + k, wv);
+      for (int c = 0; c < HF_COLS; ++c)
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int r = 0; r < HF_ROWS; ++r) acc[c][r] = 0.f;
+      for (int k = lane * 8; k < K; k += 256) {
+        float wv[HF_COLS][8];
 #pragma unroll
-          for (int r = 0; r < HF_ROWS; ++r) acc[r] = fmaf(a_sh[r * K + k + i], wv[i], acc[r]);
+        for (int c = 0; c < HF_COLS; ++c) {
+          if (n0 + c < N) load_w8<TW>(wh + (size_t)(n0 + c) * w_n + k, wv[c]);
+          else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wv[c][i] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < HF_ROWS; ++r) {
+          const float4 lo = *reinterpret_cast<const float4*>(a_sh + r * K + k), hi = *reinterpret_cast<const float4*>(a_sh + r * K + k + 4);
+          const float av[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+          for (int c = 0; c < HF_COLS; ++c)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[c][r] = fmaf(av[i], wv[c][i], acc[c][r]);
+        }
       }
+#pragma unroll
+      for (int c = 0; c < HF_COLS; ++c)
+#pragma unroll
+        for (int r = 0; r < HF_ROWS; ++r) {
+          float v = acc[c][r];
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+          if (lane == 0 && r < rows && n0 + c < N) {
+            const float g = gate ? gate[(size_t)(t0 + r) * gridDim.y + h] : 1.f;
+            out[(size_t)(t0 + r) * o_t + (size_t)h * o_h + n0 + c] = from_f32<TO>(v * g);
+          }
+        }
     } else {
-#pragma unroll 8
-      for (int k = 0; k < K; ++k) {
-        const float wv = to_f32<TW>(wp[(size_t)k * w_k]);
+      float* part_s = a_sh + HF_ROWS * K;
+      const int n = blockIdx.x * 32 + lane;
+      const int per_warp = (K + 3) / 4, k_lo = warp * per_warp, k_hi = min(K, k_lo + per_warp);
+      float acc[HF_ROWS];
 #pragma unroll
-        for (int r = 0; r < HF_ROWS; ++r) acc[r] = fmaf(a_sh[r * K + k], wv, acc[r]);
+      for (int r = 0; r < HF_ROWS; ++r) acc[r] = 0.f;
+      if (n < N) {
+        const TW* wp = wh + (size_t)n * w_n;
+#pragma unroll 8
+        for (int k = k_lo; k < k_hi; ++k) {
+          const float wv = to_f32<TW>(wp[(size_t)k * w_k]);
+#pragma unroll
+          for (int r = 0; r < HF_ROWS; ++r) acc[r] = fmaf(a_sh[r * K + k], wv, acc[r]);
+        }
       }
-    }
-    for (int r = 0; r < rows; ++r) {
-      const float g = gate ? gate[(size_t)(t0 + r) * gridDim.y + h] : 1.f;
-      out[(size_t)(t0 + r) * o_t + (size_t)h * o_h + n] = from_f32<TO>(acc[r] * g);
+#pragma unroll
+      for (int r = 0; r < HF_ROWS; ++r) part_s[(warp * HF_ROWS + r) * 32 + lane] = acc[r];
+      __syncthreads();
+      for (int e = threadIdx.x; e < HF_ROWS * 32; e += HF_THREADS) {
+        const int r = e / 32, c = e % 32;
+        if (r < rows && blockIdx.x * 32 + c < N) {
+          float v = 0.f;
+#pragma unroll
+          for (int p = 0; p < 4; ++p) v += part_s[(p * HF_ROWS + r) * 32 + c];
+          const float g = gate ? gate[(size_t)(t0 + r) * gridDim.y + h] : 1.f;
+          out[(size_t)(t0 + r) * o_t + (size_t)h * o_h + blockIdx.x * 32 + c] = from_f32<TO>(v * g);
+        }
+      }
     }
   }
 }
@@ -140,16 +190,19 @@ extern "C" int lse_head_gemm(const void* a, int a_dtype, long long a_t, long lon
   if (heads <= 0 || heads > 65535 || N <= 0 || K <= 0) return LSE_ERR_BAD_ARGUMENT;
   dim3 grid((N + HG_TILE - 1) / HG_TILE, (T + HG_TILE - 1) / HG_TILE, heads);
   if (grid.y > 65535) return LSE_ERR_TOO_LARGE;
-  const bool few = T <= 32 && (size_t)HF_ROWS * K * sizeof(float) <= 48 * 1024;
-  const dim3 few_grid((N + HF_THREADS - 1) / HF_THREADS, heads);
-  const size_t few_smem = (size_t)HF_ROWS * K * sizeof(float);
+  const size_t few_smem = (size_t)HF_ROWS * (K + 4 * 32) * sizeof(float);
+  const bool few = T <= 32 && few_smem <= 48 * 1024;
   const size_t w_bytes = w_dtype == LSE_DTYPE_BF16 ? 2 : 4;
-  const int vector_k = (w_k == 1 && K % 8 == 0 && (w_h * w_bytes) % 16 == 0 && (w_n * w_bytes) % 16 == 0 &&
-                        ((uintptr_t)w & 15) == 0) ? 1 : 0;
+  const bool k_side = w_k == 1 && K % 8 == 0 && (w_h * w_bytes) % 16 == 0 && (w_n * w_bytes) % 16 == 0 &&
+                      ((uintptr_t)w & 15) == 0;
+  const dim3 few_grid(k_side ? (N + 4 * HF_COLS - 1) / (4 * HF_COLS) : (N + 31) / 32, heads);
 #define LSE_HG_CASE(TA, TW, TO)                                                                                 \
-  if (few)                                                                                                      \
-    lse_launch(head_gemm_few_kernel<TA, TW, TO>, few_grid, HF_THREADS, few_smem, stream, (const TA*)a, a_t, a_h, \
-               (const TW*)w, w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K, vector_k);                        \
+  if (few && k_side)                                                                                            \
+    lse_launch(head_gemm_few_kernel<TA, TW, TO, true>, few_grid, HF_THREADS, few_smem, stream, (const TA*)a,    \
+               a_t, a_h, (const TW*)w, w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K);                        \
+  else if (few)                                                                                                 \
+    lse_launch(head_gemm_few_kernel<TA, TW, TO, false>, few_grid, HF_THREADS, few_smem, stream, (const TA*)a,   \
+               a_t, a_h, (const TW*)w, w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K);                        \
   else                                                                                                          \
     lse_launch(head_gemm_kernel<TA, TW, TO>, grid, HG_THREADS, 0, stream, (const TA*)a, a_t, a_h, (const TW*)w,  \
                w_h, w_k, w_n, (TO*)out, o_t, o_h, gate, T, N, K);

@@ -37,8 +37,9 @@ __device__ __forceinline__ float la_act(float z, int act) { return act == 1 ? z 
 //     chunk_state[chunk].  phase 2: from chunk_state[chunk] (which linear_attention_carry_kernel has turned into the
 //     state at the chunk's start), outputs written, the state is not stored.
 // Chunks are what lets a long prompt use the whole GPU: a request's rows are walked in order only within a chunk.
-template <typename TD, int PARTS>
-__global__ void __launch_bounds__(LA_THREADS)
+// OUTPUTS false: the pass that only builds a chunk's own state (phase 1) leaves the output's half of the work out.
+template <typename TD, int PARTS, bool OUTPUTS>
+__global__ void __launch_bounds__(LA_THREADS, 4)     // four blocks an SM (measured faster than three blocks without the few spills)
 linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld,
                              int q_off, int k_off, int v_off, const float* __restrict__ decay,
                              float* __restrict__ state, const int* __restrict__ segment_start,
@@ -89,7 +90,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       ? state + ((size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * heads + h) * dim * vdim
       : chunk_state + ((size_t)blockIdx.x * heads + h) * dim * vdim;
   const bool from_zero = chunk_rows > 0 && phase == 1;
-  const bool outputs = !(chunk_rows > 0 && phase == 1), store = !(chunk_rows > 0 && phase == 2);
+  const bool store = !(chunk_rows > 0 && phase == 2);
   float s[LA_DPT];
 #pragma unroll
   for (int i = 0; i < LA_DPT; ++i) {
@@ -145,13 +146,17 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       float o[4] = {0.f, 0.f, 0.f, 0.f};     // four short chains instead of one of 32 dependent additions
 #pragma unroll
       for (int i = 0; i < LA_DPT / 4; ++i) {
-        const float4 kq = kr[i], qq = qr[i];
-        s[4 * i + 0] = fmaf(dk, s[4 * i + 0], kq.x * vv); o[0] = fmaf(s[4 * i + 0], qq.x, o[0]);
-        s[4 * i + 1] = fmaf(dk, s[4 * i + 1], kq.y * vv); o[1] = fmaf(s[4 * i + 1], qq.y, o[1]);
-        s[4 * i + 2] = fmaf(dk, s[4 * i + 2], kq.z * vv); o[2] = fmaf(s[4 * i + 2], qq.z, o[2]);
-        s[4 * i + 3] = fmaf(dk, s[4 * i + 3], kq.w * vv); o[3] = fmaf(s[4 * i + 3], qq.w, o[3]);
+        const float4 kq = kr[i], qq = OUTPUTS ? qr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        s[4 * i + 0] = fmaf(dk, s[4 * i + 0], kq.x * vv);
+        s[4 * i + 1] = fmaf(dk, s[4 * i + 1], kq.y * vv);
+        s[4 * i + 2] = fmaf(dk, s[4 * i + 2], kq.z * vv);
+        s[4 * i + 3] = fmaf(dk, s[4 * i + 3], kq.w * vv);
+        if (OUTPUTS) {
+          o[0] = fmaf(s[4 * i + 0], qq.x, o[0]); o[1] = fmaf(s[4 * i + 1], qq.y, o[1]);
+          o[2] = fmaf(s[4 * i + 2], qq.z, o[2]); o[3] = fmaf(s[4 * i + 3], qq.w, o[3]);
+        }
       }
-      if (outputs) {
+      if (OUTPUTS) {
         float total = (o[0] + o[1]) + (o[2] + o[3]);
 #pragma unroll
         for (int off = CW; off < 32; off <<= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
@@ -193,16 +198,20 @@ linear_attention_carry_kernel(const float* __restrict__ decay, float* __restrict
   float* slot = state + (size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * per_state + e;
   float running = *slot;
   const int chunks = (b - a + chunk_rows - 1) / chunk_rows;
-  for (int c = 0; c < chunks; ++c) {
-    float* own = chunk_state + (size_t)(before + c) * per_state + e;
-    const float mine = *own;
-    *own = running;
-    float power = full;
-    if (c == chunks - 1) {
-      power = 1.f;
-      for (int i = 0; i < b - a - c * chunk_rows; ++i) power *= dk;
+  float last_power = 1.f;
+  for (int i = 0; i < b - a - (chunks - 1) * chunk_rows; ++i) last_power *= dk;
+  float* own = chunk_state + (size_t)before * per_state + e;
+  for (int c0 = 0; c0 < chunks; c0 += 8) {      // eight chunks' states are fetched together, then carried in order
+    float mine[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mine[i] = c0 + i < chunks ? own[(size_t)(c0 + i) * per_state] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (c0 + i < chunks) {
+        own[(size_t)(c0 + i) * per_state] = running;
+        running = fmaf(c0 + i == chunks - 1 ? last_power : full, running, mine[i]);
+      }
     }
-    running = fmaf(power, running, mine);
   }
   *slot = running;
 }
@@ -248,9 +257,16 @@ extern "C" int lse_linear_attention_scan(const void* proj, int proj_dtype, int n
     const int cb = 4 * (32 / P);                                                                                 \
     dim3 grid(chunk_rows ? max_chunks : max_segments, heads, (vdim + cb - 1) / cb);                              \
     for (int phase = 1; phase <= (chunk_rows ? 2 : 1); ++phase) {                                                \
-      lse_launch(linear_attention_scan_kernel<TD, P>, grid, LA_THREADS, 0, stream, (const TD*)proj, n_partials,  \
-                 partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start, segment_slot, out, heads, \
-                 dim, vdim, act, num_slots, max_segments, chunk_rows, phase, chunk_state);                       \
+      if (chunk_rows && phase == 1)                                                                              \
+        lse_launch(linear_attention_scan_kernel<TD, P, false>, grid, LA_THREADS, 0, stream, (const TD*)proj,     \
+                   n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start,             \
+                   segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, phase,         \
+                   chunk_state);                                                                                 \
+      else                                                                                                       \
+        lse_launch(linear_attention_scan_kernel<TD, P, true>, grid, LA_THREADS, 0, stream, (const TD*)proj,      \
+                   n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start,             \
+                   segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, phase,         \
+                   chunk_state);                                                                                 \
       if (chunk_rows && phase == 1) {                                                                            \
         const size_t per_state = (size_t)heads * dim * vdim;                                                     \
         lse_launch(linear_attention_carry_kernel, dim3((unsigned)((per_state + 255) / 256), max_segments), 256,  \

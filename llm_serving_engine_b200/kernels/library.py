@@ -26,7 +26,7 @@ _SIGNATURES = {
                           c_int, c_int, c_float, c_void_p, c_void_p],
     "lse_latent_prepare": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int,
                            c_int, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
-                           c_int, c_int, c_void_p, c_float, c_int, c_int, c_void_p],
+                           c_int, c_int, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
     "lse_latent_query": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p,
                          c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lse_latent_attention_chunk": [],

@@ -638,7 +638,7 @@ def latent_prepare(proj: torch.Tensor, positions: torch.Tensor, slot_mapping: to
                                  _ptr(q_latent), kv_off, rank, _ptr(kv_norm), rot, rot_dims, _ptr(freq),
                                  float(rot_factor), positions.data_ptr(), slot_mapping.data_ptr(), _ptr(cache),
                                  dtype_code(out_dtype), g_off, heads, _ptr(gate), float(eps), tokens, num_slots,
-                                 _stream()), "latent_prepare")
+                                 proj.shape[-1], _stream()), "latent_prepare")
 
 
 def latent_query(proj: torch.Tensor, q_off: int, heads: int, dim: int, rot: int, rot_dims: int, freq: torch.Tensor,
