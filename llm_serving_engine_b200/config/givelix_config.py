@@ -76,8 +76,8 @@ class GivelixConfig:
                 if not 0 <= int(source) < index or self.layers[int(source)].get("type") not in MIXER_TYPES[1:]:
                     raise ConfigError(f"layer {index}: kv_from must name an earlier latent attention layer")
                 other = self.layers[int(source)]["mixer"]
-                if other.get("kv_from") is not None or any(other[key] != mixer[key] for key in ("kv_rank", "rot_dim", "rot")):
-                    raise ConfigError(f"layer {index}: layer {source} must own a cache with the same kv_rank, rot_dim and rot")
+                if other.get("kv_from") is not None or any(int(other[key]) != int(mixer[key]) for key in ("kv_rank", "rot_dim")):
+                    raise ConfigError(f"layer {index}: layer {source} must own a cache with the same kv_rank and rot_dim")
             mlp = layer.get("mlp")
             if mlp is not None and (mlp.get("kind", "dense") != "dense" or int(mlp.get("ff", 0)) <= 0):
                 raise ConfigError(f"layer {index}: the feed-forward must be dense with a positive ff")

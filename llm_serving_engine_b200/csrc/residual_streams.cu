@@ -84,21 +84,11 @@ streams_update_rmsnorm_kernel(float* __restrict__ X, const TD* __restrict__ delt
     float u[4] = {0.f, 0.f, 0.f, 0.f};
     if (del) {
       float y[4] = {0.f, 0.f, 0.f, 0.f};
-      if (n_partials == 1) {
-        rs_load<TD>(del + h, y, VEC);
-      } else {
-        for (int p0 = 0; p0 < n_partials; p0 += 8) {    // eight partial sums a round trip, added in index order
-          float part[8][4];
+      for (int p = 0; p < n_partials; ++p) {
+        float part[4];
+        rs_load<TD>(del + (size_t)p * partial_stride + h, part, VEC);
 #pragma unroll
-          for (int p = 0; p < 8; ++p)
-            if (p0 + p < n_partials) rs_load<TD>(del + (size_t)(p0 + p) * partial_stride + h, part[p], VEC);
-#pragma unroll
-          for (int p = 0; p < 8; ++p)
-            if (p0 + p < n_partials) {
-#pragma unroll
-              for (int e = 0; e < VEC; ++e) y[e] += part[p][e];
-            }
-        }
+        for (int e = 0; e < VEC; ++e) y[e] += part[e];
       }
       float sc[4] = {1.f, 1.f, 1.f, 1.f};
       if (scale) rs_load<float>(scale + h, sc, VEC);
