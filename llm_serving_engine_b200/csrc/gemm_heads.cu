@@ -103,6 +103,8 @@ head_gemm_few_kernel(const TA* __restrict__ a, long long a_t, long long a_h, con
   for (int t0 = 0; t0 < T; t0 += HF_ROWS) {
     const int rows = min(HF_ROWS, T - t0);
     __syncthreads();
+    // unrolled so that several loads are in flight before the first store waits for its value
+#pragma unroll 8
     for (int e = threadIdx.x; e < HF_ROWS * K; e += HF_THREADS) {
       const int r = e / K, k = e % K;
       a_sh[e] = r < rows ? to_f32<TA>(a[(size_t)(t0 + r) * a_t + (size_t)h * a_h + k]) : 0.f;
