@@ -60,12 +60,15 @@ CONFIGS = {
                           lightning(heads=1, dim=32, vdim=32, decay=(0.9,), mlp=DENSE)], width=64, streams=1, mult=1.0,
                          logit_scale=1.0),
     # sizes that no vector load, tensor-core tile or few-rows product takes: every kernel's plain path
-    "odd_sizes": model([latent(heads=5, dim=20, rot_dim=6, vdim=12, kv_rank=36, q_rank=30, rot={"base": 777.0, "dims": 6},
+    "odd_sizes": model([lightning(heads=2, dim=48, vdim=20, decay=(0.7, 0.99)),
+                        latent(heads=5, dim=20, rot_dim=6, vdim=12, kv_rank=36, q_rank=30, rot={"base": 777.0, "dims": 6},
                                mlp={"kind": "dense", "ff": 90}),
-                        lightning(heads=2, dim=48, vdim=20, decay=(0.7, 0.99)),
                         latent2(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=22,
                                 rot={"base": 1000.0, "dims": 6, "scaling": {"factor": 3.0, "original": 40, "fast": 8.0, "slow": 1.0}},
-                                mlp={"kind": "dense", "ff": 50})], width=100, vocab=333, streams=2),
+                                mlp={"kind": "dense", "ff": 50}),
+                        # a reader of a cache that is not the first layer's, with other heads and sizes of its own
+                        latent(heads=9, dim=8, rot_dim=6, vdim=10, kv_rank=36, q_rank=14, rot={"base": 777.0, "dims": 6}, kv_from=1)],
+                       width=102, vocab=333, streams=2),
 }
 NO_LAYER_SCALE = {"equal_sizes"}
 # bfloat16: the random models are made with large gains so that every mechanism matters; their rounding noise is
