@@ -87,6 +87,8 @@ class CacheGroup:
     storage: torch.Tensor | None = None           # [len(layers), 2, pages, kv heads, page_size, head size], or
                                                   # [len(layers), 1, pages, page_size, width] for latent rows
     layer_slot: dict[int, int] = field(default_factory=dict)
+    value_storage: torch.Tensor | None = None     # [len(layers), pages, kv heads, page_size, value size] when values
+                                                  # have a size of their own (storage then holds the keys alone)
 
 
 @dataclass
@@ -169,9 +171,14 @@ class CacheManager:
         for group in self.groups:
             if isinstance(group.need, PagedLatent):
                 shape = (len(group.layers), 1, config.num_blocks, self.page_size, group.need.width)
-            else:
+            elif group.need.value_dim in (0, group.need.head_dim):
                 shape = (len(group.layers), 2, config.num_blocks, group.need.num_kv_heads, self.page_size,
                          group.need.head_dim)
+            else:
+                shape = (len(group.layers), 1, config.num_blocks, group.need.num_kv_heads, self.page_size,
+                         group.need.head_dim)
+                group.value_storage = torch.zeros(shape[:1] + shape[2:5] + (group.need.value_dim,), dtype=dtype,
+                                                  device=self.device)
             group.storage = torch.zeros(shape, dtype=dtype, device=self.device)
 
     # -- requests ----------------------------------------------------------------
@@ -322,6 +329,8 @@ class CacheManager:
             storage = group.storage[group.layer_slot[source]]
             view.keys, view.group = storage[0], group_index     # latent rows: [pages, page_size, width], no values
             view.values = storage[1] if storage.shape[0] > 1 else None
+            if group.value_storage is not None:
+                view.values = group.value_storage[group.layer_slot[source]]
         if source in self.states.tensors:
             view.state = self.states.tensors[source]
         return view
@@ -329,7 +338,7 @@ class CacheManager:
     # -- statistics ------------------------------------------------------------
     def bytes_per_page(self, group: CacheGroup) -> int:
         per_token = (group.need.width if isinstance(group.need, PagedLatent)
-                     else 2 * group.need.num_kv_heads * group.need.head_dim)
+                     else group.need.num_kv_heads * (group.need.head_dim + (group.need.value_dim or group.need.head_dim)))
         return len(group.layers) * self.page_size * per_token * torch.empty((), dtype=self.dtype).element_size()
 
     def kv_bytes_per_token(self) -> int:

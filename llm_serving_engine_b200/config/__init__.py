@@ -1,3 +1,4 @@
+from .fororax_config import FororaxConfig
 from .givelix_config import GivelixConfig
 from .model_config import ConfigError, LayerSpec, ModelSpec, PartSpec, Qwen2Config
 from .registry import (Architecture, known_architectures, load_config, register_architecture,
@@ -5,7 +6,7 @@ from .registry import (Architecture, known_architectures, load_config, register_
 from .runtime_config import CacheConfig, SchedulerConfig
 
 __all__ = [
-    "Architecture", "CacheConfig", "ConfigError", "GivelixConfig", "LayerSpec", "ModelSpec", "PartSpec",
+    "Architecture", "CacheConfig", "ConfigError", "FororaxConfig", "GivelixConfig", "LayerSpec", "ModelSpec", "PartSpec",
     "Qwen2Config", "SchedulerConfig", "known_architectures", "load_config",
     "register_architecture", "resolve_architecture",
 ]

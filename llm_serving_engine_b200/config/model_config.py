@@ -65,6 +65,9 @@ class ModelSpec:
     max_position_embeddings: int
     residual_streams: int = 1        # copies of the residual (hyper-connections); read as their sum at the end
     logit_scale: float = 1.0         # the logits are multiplied by it
+    embedding_scale: float = 1.0     # the embedding rows are multiplied by it
+    position_table_name: str | None = None   # a learned vector per position [max_position_embeddings, hidden], added to the embedding
+    logit_softcap: float = 0.0       # > 0: logits <- cap * tanh(logits / cap)
 
     def __post_init__(self) -> None:
         for index in self.order:

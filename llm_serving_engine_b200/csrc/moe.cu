@@ -1,0 +1,155 @@
+// Mixture of experts: the router and the experts' gated activation.
+//
+// Router (one block per token, everything float32): z_e = w_e . x over all router outputs (the last `identity` of
+// them are identity experts, whose output is the token's input itself), s = softmax(z), the `top` outputs with the
+// largest s_e + correction_e are chosen (ties: the lower index), and a chosen output's weight is s_e itself, neither
+// corrected nor renormalised.  The kernel leaves a dense row of weights over the real experts (zero where an expert
+// was not chosen), the sum of the chosen identity experts' weights, and the gate of the shared expert,
+// sigmoid(w_sg . x).
+//
+// Activation (experts side by side in one product): the row of `gate_up` is [gate (I values) | up (I values)], where
+// the I columns are `experts` blocks of `ff` columns followed by `shared_ff` columns of the shared expert:
+//   g = min(gate, limit);  u = clamp(up, -limit, limit);  out = c * g * sigmoid(1.702 g) * (u + 1)
+// with c the token's weight of the column's expert (the shared gate for the shared columns).  The down product over
+// all I columns then is the weighted sum over the experts.
+#include "common.cuh"
+
+namespace {
+constexpr int ROUTE_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_kernel(const T* __restrict__ x, const T* __restrict__ router, const float* __restrict__ correction,
+                 const T* __restrict__ shared_gate_w, float* __restrict__ expert_weights,
+                 float* __restrict__ identity_weight, float* __restrict__ shared_gate, int* __restrict__ chosen_out,
+                 int width, int outputs, int identity, int top) {
+  extern __shared__ float smem[];   // [outputs] scores, [outputs] choice scores
+  pdl_launch_dependents();
+  pdl_wait();
+  float* score = smem;
+  float* choice = smem + outputs;
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* row = x + (size_t)t * width;
+  for (int e = warp; e < outputs + (shared_gate_w ? 1 : 0); e += ROUTE_THREADS / 32) {
+    const T* w = e < outputs ? router + (size_t)e * width : shared_gate_w;
+    float sum = 0.f;
+    for (int i = lane; i < width; i += 32) sum = fmaf(to_f32<T>(row[i]), to_f32<T>(w[i]), sum);
+    sum = warp_sum(sum);
+    if (lane == 0) {
+      if (e < outputs) score[e] = sum;
+      else shared_gate[t] = 1.0f / (1.0f + expf(-sum));
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  const int experts = outputs - identity;
+  float top_z = -INFINITY;
+  for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, score[e]);
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+  for (int e = lane; e < outputs; e += 32) sum += expf(score[e] - top_z);
+  sum = warp_sum(sum);
+  for (int e = lane; e < outputs; e += 32) {
+    const float s = expf(score[e] - top_z) / sum;
+    score[e] = s;
+    choice[e] = correction ? s + correction[e] : s;
+    if (e < experts) expert_weights[(size_t)t * experts + e] = 0.f;
+  }
+  __syncwarp();
+  float identity_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < outputs; e += 32) {
+      const float c = choice[e];
+      if (c > best) { best = c; best_e = e; }   // ascending e within a lane: the first largest stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+    if (best_e >= outputs) break;   // fewer outputs than `top`
+    if (lane == 0) {
+      choice[best_e] = -INFINITY;
+      if (best_e < experts) expert_weights[(size_t)t * experts + best_e] = score[best_e];
+      if (chosen_out) chosen_out[(size_t)t * top + k] = best_e;
+    }
+    if (best_e >= experts) identity_sum += score[best_e];
+    __syncwarp();
+  }
+  if (lane == 0) identity_weight[t] = identity_sum;
+}
+
+template <typename TI, typename TO>
+__global__ void moe_gated_act_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
+                                     const float* __restrict__ expert_weights, const float* __restrict__ shared_gate,
+                                     TO* __restrict__ out, int experts, int ff, int shared_ff, float limit,
+                                     float shared_limit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int inter = experts * ff + shared_ff;
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= inter) return;
+  const bool shared = i >= experts * ff;
+  const float c = shared ? (shared_gate ? shared_gate[t] : 1.f) : expert_weights[(size_t)t * experts + i / ff];
+  TO* dst = out + (size_t)t * inter + i;
+  if (c == 0.f) { *dst = from_f32<TO>(0.f); return; }   // an expert that the token did not choose
+  const TI* row = gate_up + (size_t)t * 2 * inter;
+  float g = 0.f, u = 0.f;
+  for (int p = 0; p < n_partials; ++p) {
+    g += to_f32<TI>(row[(size_t)p * partial_stride + i]);
+    u += to_f32<TI>(row[(size_t)p * partial_stride + inter + i]);
+  }
+  const float lim = shared ? shared_limit : limit;
+  g = fminf(g, lim);
+  u = fminf(fmaxf(u, -lim), lim);
+  const float act = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  *dst = from_f32<TO>(c * act);
+}
+}  // namespace
+
+// x, router [outputs, width], shared_gate_w [width] (or null) in one dtype; correction float32 [outputs] or null.
+// expert_weights float32 [tokens, outputs - identity]; identity_weight, shared_gate float32 [tokens];
+// chosen int32 [tokens, top] or null.
+extern "C" int lse_moe_route(const void* x, const void* router, const float* correction, const void* shared_gate_w,
+                             int dtype, float* expert_weights, float* identity_weight, float* shared_gate, int* chosen,
+                             int tokens, int width, int outputs, int identity, int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (outputs <= 0 || identity < 0 || identity > outputs || top <= 0 || width <= 0) return LSE_ERR_BAD_ARGUMENT;
+  if (outputs > 4096) return LSE_ERR_TOO_LARGE;
+  const size_t smem = sizeof(float) * 2 * (size_t)outputs;
+  if (dtype == LSE_DTYPE_F32)
+    lse_launch(moe_route_kernel<float>, tokens, ROUTE_THREADS, smem, stream, (const float*)x, (const float*)router,
+               correction, (const float*)shared_gate_w, expert_weights, identity_weight, shared_gate, chosen, width,
+               outputs, identity, top);
+  else if (dtype == LSE_DTYPE_BF16)
+    lse_launch(moe_route_kernel<__nv_bfloat16>, tokens, ROUTE_THREADS, smem, stream, (const __nv_bfloat16*)x,
+               (const __nv_bfloat16*)router, correction, (const __nv_bfloat16*)shared_gate_w, expert_weights,
+               identity_weight, shared_gate, chosen, width, outputs, identity, top);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
+                                 const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
+                                 int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,
+                                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int inter = experts * ff + shared_ff;
+  if (inter <= 0 || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
+  if ((inter + 255) / 256 > 65535) return LSE_ERR_TOO_LARGE;
+  const dim3 grid(tokens, (inter + 255) / 256);
+#define LSE_MOE_ACT_CASE(TI, TO)                                                                                   \
+  lse_launch(moe_gated_act_kernel<TI, TO>, grid, 256, 0, stream, (const TI*)gate_up, n_partials, partial_stride,   \
+             expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit)
+  if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_MOE_ACT_CASE(float, float);
+  else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_MOE_ACT_CASE(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_MOE_ACT_CASE(float, __nv_bfloat16);
+  else return LSE_ERR_BAD_ARGUMENT;
+#undef LSE_MOE_ACT_CASE
+  LSE_LAUNCH_CHECK();
+}

@@ -732,3 +732,191 @@ def head_gemm(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gate: to
                             out.data_ptr(), dtype_code(out.dtype), out.stride(0), out.stride(1), _ptr(gate), tokens,
                             heads, n, k, _stream()), "head_gemm")
     return out
+
+
+# ------------------------------------------------------------------ learned positions, norm after the sum, soft cap
+def embedding_positions(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                        scale: float, residual: torch.Tensor, hidden_out: torch.Tensor | None) -> None:
+    """residual[t] = table[ids[t]] * scale + pos_table[positions[t]] in float32; ``hidden_out`` (the tables' dtype, or
+    None) receives the same rows rounded."""
+    _need_cuda(table, pos_table, ids, positions, residual, hidden_out)
+    vocab, hidden = table.shape
+    assert pos_table.dtype == table.dtype and pos_table.shape[1] == hidden and table.is_contiguous() and pos_table.is_contiguous()
+    assert ids.dtype == torch.int32 and positions.dtype == torch.int32 and residual.dtype == torch.float32
+    assert residual.shape == (ids.shape[0], hidden) and residual.is_contiguous()
+    assert hidden_out is None or (hidden_out.shape == residual.shape and hidden_out.dtype == table.dtype and hidden_out.is_contiguous())
+    check(library.load().lse_embedding_positions(table.data_ptr(), pos_table.data_ptr(), dtype_code(table.dtype),
+                                                 ids.data_ptr(), positions.data_ptr(), float(scale), residual.data_ptr(),
+                                                 _ptr(hidden_out), ids.shape[0], hidden, vocab, pos_table.shape[0],
+                                                 _stream()), "embedding_positions")
+
+
+def scaled_add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, bias: torch.Tensor | None,
+                       row_scale: torch.Tensor | None, alpha: float, weight: torch.Tensor, eps: float,
+                       hidden_io: torch.Tensor | None) -> None:
+    """residual <- rmsnorm(alpha * residual + delta + bias + row_scale[t] * x_t) * weight, where x_t is the row's value in
+    ``hidden_io`` (the residual's copy in the compute dtype, overwritten with the new rows; None: the residual itself
+    is the only copy).  delta [T, H], a float32 stack of partial sums [P, T, H], or None; bias float32 [H] or None."""
+    _need_cuda(residual, delta, bias, row_scale, weight, hidden_io)
+    tokens, hidden = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and weight.dtype == torch.float32 and weight.shape == (hidden,)
+    assert bias is None or (bias.dtype == torch.float32 and bias.shape == (hidden,))
+    assert row_scale is None or (row_scale.dtype == torch.float32 and row_scale.shape[0] >= tokens and row_scale.is_contiguous())
+    assert hidden_io is None or (hidden_io.shape == residual.shape and hidden_io.is_contiguous())
+    delta, n_partials, stride = _partials(delta, tokens, hidden)
+    out_code = dtype_code(hidden_io.dtype) if hidden_io is not None else F32
+    delta_code = dtype_code(delta.dtype) if delta is not None else out_code
+    check(library.load().lse_scaled_add_rmsnorm(residual.data_ptr(), _ptr(delta), delta_code, n_partials, stride, _ptr(bias),
+                                                _ptr(row_scale), float(alpha), weight.data_ptr(), _ptr(hidden_io), out_code,
+                                                tokens, hidden, float(eps), _stream()), "scaled_add_rmsnorm")
+
+
+def softcap(values: torch.Tensor, cap: float) -> torch.Tensor:
+    """values <- cap * tanh(values / cap), in place (float32)."""
+    _need_cuda(values)
+    assert values.dtype == torch.float32 and values.is_contiguous()
+    check(library.load().lse_softcap(values.data_ptr(), values.numel(), float(cap), _stream()), "softcap")
+    return values
+
+
+def add_scaled_rows(y: torch.Tensor, row_scale: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """y[t] += row_scale[t] * x[t]; y, x [T, H]; row_scale float32 [T]."""
+    _need_cuda(y, row_scale, x)
+    assert y.shape == x.shape and y.is_contiguous() and x.is_contiguous() and row_scale.dtype == torch.float32
+    check(library.load().lse_add_scaled_rows(y.data_ptr(), dtype_code(y.dtype), row_scale.data_ptr(), x.data_ptr(),
+                                             dtype_code(x.dtype), y.shape[0], y.shape[1], _stream()), "add_scaled_rows")
+    return y
+
+
+# ------------------------------------------------------------------ attention with normed heads and changed scores
+def head_norm_kv_write(proj: torch.Tensor, bias: torch.Tensor | None, q_norm: torch.Tensor | None,
+                       k_norm: torch.Tensor | None, eps: float, slot_mapping: torch.Tensor | None, q_out: torch.Tensor,
+                       k_cache: torch.Tensor | None, v_cache: torch.Tensor | None, n_q: int, n_kv: int, dk: int,
+                       dv: int) -> None:
+    """From a row [q (n_q * dk) | k (n_kv * dk) | v (n_kv * dv) | ...] of ``proj`` (+ ``bias``): every query head
+    RMS-normed with ``q_norm`` [dk] into ``q_out`` [T, n_q, dk]; every key head normed with ``k_norm`` and every value
+    head as it is into the row's place in the pages (k_cache [pages, n_kv, page, dk], v_cache [.., dv]).  ``n_kv`` = 0:
+    queries only (a layer that reads another layer's pages)."""
+    _need_cuda(proj, bias, q_norm, k_norm, slot_mapping, q_out, k_cache, v_cache)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert q_out.shape == (tokens, n_q, dk) and q_out.is_contiguous()
+    assert bias is None or bias.dtype == torch.float32
+    for weight in (q_norm, k_norm):
+        assert weight is None or (weight.dtype == torch.float32 and weight.shape == (dk,))
+    page_size = num_pages = 0
+    if n_kv:
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype == q_out.dtype
+        assert k_cache.shape[1] == n_kv and k_cache.shape[3] == dk and v_cache.shape[3] == dv
+        assert slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] >= tokens
+        num_pages, page_size = k_cache.shape[0], k_cache.shape[2]
+    check(library.load().lse_head_norm_kv_write(proj.data_ptr(), code, n_partials, stride, ld, _ptr(bias), _ptr(q_norm),
+                                                _ptr(k_norm), float(eps), _ptr(slot_mapping), q_out.data_ptr(),
+                                                _ptr(k_cache) if n_kv else None, _ptr(v_cache) if n_kv else None,
+                                                dtype_code(q_out.dtype), tokens, n_q, n_kv, dk, dv, page_size, num_pages,
+                                                _stream()), "head_norm_kv_write")
+
+
+def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                     block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
+                     r1: torch.Tensor | None = None, r2: torch.Tensor | None = None, sink: torch.Tensor | None = None,
+                     cross: bool = False, split: bool | None = None) -> torch.Tensor:
+    """Causal attention of every row of the step over its request's pages, with the scores or weights changed:
+    s_ij = q_i . k_j * scale - r1_h ln(1 + r2_h (i - j)) (``r1``, ``r2`` float32 [n_q]); exp(sink_h) in the
+    denominator (``sink`` float32 [n_q]).  q [T, n_q, dk]; k_cache [pages, n_kv, page, dk]; v_cache [.., dv];
+    out [T, n_q, dv], or with ``cross`` [T, n_q, n_kv, dv]: head h's weights applied to the values of every
+    key/value head.  ``out`` is in the cache's dtype or float32.  ``split`` as for :func:`paged_attention_generic`."""
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions, r1, r2, sink)
+    tokens, n_q, dk = q.shape
+    n_kv, page_size, dv = k_cache.shape[1], k_cache.shape[2], v_cache.shape[3]
+    n_values = n_kv if cross else 1
+    if dk > 256 or dv > 256:
+        raise KernelError(f"attention: head sizes {dk}, {dv} beyond 256")
+    if n_q % n_kv:
+        raise KernelError(f"attention: {n_q} query heads do not divide into {n_kv} groups")
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert out.numel() == tokens * n_q * n_values * dv and out.dtype in (q.dtype, torch.float32)
+    assert q.dtype == k_cache.dtype == v_cache.dtype and k_cache.shape[3] == dk and v_cache.shape[:3] == k_cache.shape[:3]
+    assert block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1
+    for vector in (r1, r2, sink):
+        assert vector is None or (vector.dtype == torch.float32 and vector.shape == (n_q,))
+    lib = library.load()
+    partials, max_chunks = None, 0
+    if split if split is not None else tokens <= GENERIC_SPLIT_MAX_ROWS:
+        chunk = int(lib.lse_attention_scored_chunk())
+        max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
+        partials = torch.empty(tokens * n_q * n_values * max_chunks * (dv + 2), dtype=torch.float32, device=q.device)
+    check(lib.lse_attention_scored(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
+                                   int(out.dtype == torch.float32 and q.dtype != torch.float32), block_tables.data_ptr(),
+                                   block_tables.stride(0), segment_of_token.data_ptr(), positions.data_ptr(), _ptr(r1),
+                                   _ptr(r2), _ptr(sink), tokens, n_q, n_kv, dk, dv, int(cross), page_size, float(scale),
+                                   k_cache.shape[0], block_tables.shape[0], _ptr(partials), max_chunks, _stream()),
+          "attention_scored")
+    return out
+
+
+def head_mix_gate(wide: torch.Tensor, mix: torch.Tensor | None, gate_proj: torch.Tensor | None, gate_offset: int,
+                  gate_bias: torch.Tensor | None, segment_of_token: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
+                  dv: int) -> torch.Tensor:
+    """out[t, h] = sigmoid(gate)[t, h] * sum_g mix[h, g] * wide[t, g, slot of h]: ``wide`` float32 [T, n_q, n_kv, dv]
+    (the output of :func:`attention_scored` with ``cross``; the slot of h is its own key/value head) or [T, n_q, dv];
+    ``mix`` float32 [n_q, n_q] or None; the gate's pre-activation is columns ``gate_offset`` .. + n_q * dv of
+    ``gate_proj`` (+ ``gate_bias`` float32 [n_q * dv]), or None for no gate; out [T, n_q * dv]."""
+    _need_cuda(wide, mix, gate_proj, gate_bias, segment_of_token, out)
+    tokens = out.shape[0]
+    cross = wide.numel() == tokens * n_q * n_kv * dv and n_kv > 1
+    assert wide.dtype == torch.float32 and wide.is_contiguous() and wide.numel() == tokens * n_q * (n_kv if cross else 1) * dv
+    assert out.shape == (tokens, n_q * dv) and out.is_contiguous()
+    assert mix is None or (mix.dtype == torch.float32 and mix.shape == (n_q, n_q) and mix.is_contiguous())
+    code, n_partials, stride, ld, pointer = dtype_code(out.dtype), 1, 0, 0, None
+    if gate_proj is not None:
+        gate_proj, code, n_partials, stride, ld = _projection(gate_proj)
+        pointer = gate_proj.data_ptr() + gate_offset * gate_proj.element_size()
+        assert gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.shape == (n_q * dv,))
+    check(library.load().lse_head_mix_gate(wide.data_ptr(), _ptr(mix), pointer, code, n_partials, stride, ld,
+                                           _ptr(gate_bias) if gate_proj is not None else None, segment_of_token.data_ptr(),
+                                           out.data_ptr(), dtype_code(out.dtype), tokens, n_q, n_kv, int(cross), dv,
+                                           _stream()), "head_mix_gate")
+    return out
+
+
+# ------------------------------------------------------------------ mixture of experts
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, shared_gate_w: torch.Tensor | None,
+              identity: int, top: int, chosen: torch.Tensor | None = None):
+    """The router of a mixture of experts, in float32: scores softmax(x router^T) over all outputs (the last
+    ``identity`` of them identity experts), the ``top`` largest of score + ``correction`` chosen, weights the scores
+    themselves.  Returns (expert_weights float32 [T, experts], zero where not chosen; identity_weight float32 [T],
+    the chosen identity experts' weights added up; shared_gate float32 [T] = sigmoid(x . shared_gate_w), or None)."""
+    _need_cuda(x, router, correction, shared_gate_w, chosen)
+    tokens, width = x.shape
+    outputs = router.shape[0]
+    assert x.is_contiguous() and router.is_contiguous() and router.shape[1] == width and router.dtype == x.dtype
+    assert correction is None or (correction.dtype == torch.float32 and correction.shape == (outputs,))
+    assert shared_gate_w is None or (shared_gate_w.dtype == x.dtype and shared_gate_w.numel() == width and shared_gate_w.is_contiguous())
+    assert chosen is None or (chosen.dtype == torch.int32 and chosen.shape == (tokens, top) and chosen.is_contiguous())
+    expert_weights = torch.empty((tokens, outputs - identity), dtype=torch.float32, device=x.device)
+    identity_weight = torch.empty((tokens,), dtype=torch.float32, device=x.device)
+    shared_gate = torch.empty((tokens,), dtype=torch.float32, device=x.device) if shared_gate_w is not None else None
+    check(library.load().lse_moe_route(x.data_ptr(), router.data_ptr(), _ptr(correction), _ptr(shared_gate_w),
+                                       dtype_code(x.dtype), expert_weights.data_ptr(), identity_weight.data_ptr(),
+                                       _ptr(shared_gate), _ptr(chosen), tokens, width, outputs, int(identity), int(top),
+                                       _stream()), "moe_route")
+    return expert_weights, identity_weight, shared_gate
+
+
+def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_gate: torch.Tensor | None,
+                  out: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float) -> torch.Tensor:
+    """out[t, i] = c * g * sigmoid(1.702 g) * (u + 1) with g = min(gate_i, limit), u = clamp(up_i, -limit, limit), over
+    the columns of all experts side by side (``experts`` blocks of ``ff``, then ``shared_ff`` of the shared expert with
+    its own limit); c is the token's weight of the column's expert (``shared_gate`` for the shared columns).
+    ``gate_up`` is [T, 2 I] (the row is [gate | up]) or a float32 stack of partial sums."""
+    _need_cuda(gate_up, expert_weights, shared_gate, out)
+    tokens, inter = out.shape
+    assert inter == experts * ff + shared_ff and out.is_contiguous() and gate_up.shape[-1] == 2 * inter
+    gate_up, n_partials, stride = _partials(gate_up, tokens, 2 * inter)
+    assert expert_weights.dtype == torch.float32 and expert_weights.shape == (tokens, experts) and expert_weights.is_contiguous()
+    check(library.load().lse_moe_gated_act(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride,
+                                           expert_weights.data_ptr(), _ptr(shared_gate), out.data_ptr(),
+                                           dtype_code(out.dtype), tokens, experts, ff, shared_ff, float(limit),
+                                           float(shared_limit), _stream()), "moe_gated_act")
+    return out

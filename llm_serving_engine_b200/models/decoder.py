@@ -57,6 +57,8 @@ def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
                 out[prefix + local] = tensor
         for local, tensor in _block_tensors(layer, spec.hidden_size).items():
             out[layer.prefix + local] = tensor
+    if spec.position_table_name:
+        out[spec.position_table_name] = TensorSpec((spec.max_position_embeddings, spec.hidden_size))
     norm_cls = NORMS.get(spec.final_norm.kind)
     for local, tensor in norm_cls.expected_tensors(spec.final_norm.params, spec.hidden_size).items():
         out[spec.final_norm_prefix + local] = tensor
@@ -97,6 +99,7 @@ class DecoderModel:
         self.device = torch.device(device)
         self.embedding = weights[spec.embedding_name].contiguous()
         self.lm_head = self.embedding if spec.tie_word_embeddings else weights[spec.lm_head_name].contiguous()
+        self.position_table = weights[spec.position_table_name].contiguous() if spec.position_table_name else None
         self.blocks = []
         for index, layer in enumerate(spec.layers):
             ctx = BuildContext(dtype, self.device, spec.hidden_size, index, spec.max_position_embeddings)
@@ -160,8 +163,17 @@ class DecoderModel:
         tokens = step.num_tokens
         copies = self.spec.residual_streams
         residual = torch.empty((tokens, copies * self.spec.hidden_size), dtype=torch.float32, device=self.device)
-        ops.embedding(self.embedding, step.token_ids, residual, copies)   # every copy starts as the embedding
-        stream = ResidualStream(residual, copies=copies)
+        if self.position_table is not None or self.spec.embedding_scale != 1.0:
+            if copies != 1 or self.position_table is None:
+                raise ops.KernelError("a scaled embedding comes with a position table and one copy of the residual")
+            hidden = residual if self.dtype == torch.float32 else torch.empty_like(residual, dtype=self.dtype)
+            ops.embedding_positions(self.embedding, self.position_table, step.token_ids, step.positions,
+                                    self.spec.embedding_scale, residual, None if hidden is residual else hidden)
+            stream = ResidualStream(residual, copies=copies)
+            stream.hidden = hidden
+        else:
+            ops.embedding(self.embedding, step.token_ids, residual, copies)   # every copy starts as the embedding
+            stream = ResidualStream(residual, copies=copies)
         for position, index in enumerate(self.spec.order):   # caches run along the order
             self.blocks[index].forward(stream, step, caches[position])
             if self.layer_hook is not None:
@@ -173,4 +185,6 @@ class DecoderModel:
         logits = linear(x, self.lm_head, out_dtype=torch.float32)
         if self.spec.logit_scale != 1.0:
             logits.mul_(self.spec.logit_scale)
+        if self.spec.logit_softcap > 0.0:
+            ops.softcap(logits, self.spec.logit_softcap)
         return logits

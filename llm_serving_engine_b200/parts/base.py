@@ -43,11 +43,13 @@ class BuildContext:
 @dataclass(frozen=True)
 class PagedKV:
     """The mixer keeps keys and values of every token in pages.  ``window`` > 0:
-    only the last ``window`` keys are read, older pages are given back."""
+    only the last ``window`` keys are read, older pages are given back.
+    ``value_dim`` > 0: a value has this size instead of ``head_dim`` (keys and values then lie in two tensors)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -81,7 +83,8 @@ class ResidualStream:
     weights with which the next branch reads the copies.  The norm that adds the pending output
     applies all of it (``Norm.forward``)."""
 
-    __slots__ = ("residual", "delta", "copies", "delta_mult", "delta_scale", "mix", "write", "read")
+    __slots__ = ("residual", "delta", "copies", "delta_mult", "delta_scale", "mix", "write", "read", "hidden",
+                 "delta_bias")
 
     def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None, copies: int = 1) -> None:
         self.residual = residual
@@ -92,6 +95,11 @@ class ResidualStream:
         self.mix = None
         self.write = None
         self.read = None
+        # For models that normalise AFTER the sum (the residual itself is what the branches read): the residual in
+        # the compute dtype, kept up to date by the embedding and by every norm (the residual tensor itself in
+        # float32), and a bias (float32 [H]) that belongs to the pending output.
+        self.hidden = None
+        self.delta_bias = None
 
     @property
     def plain(self) -> bool:
@@ -127,6 +135,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    output_bias = None     # float32 [H]: a bias of the output projection, left to the norm that adds the output
+
     @classmethod
     def cache_requirement(cls, params: dict[str, Any], hidden_size: int):
         """``PagedKV``, ``RequestState`` or ``None``."""

@@ -72,3 +72,23 @@ class ResidualStreamsBlock(Block):
         self._branch(stream, 1, self.mixer_norm, lambda x: self.mixer.forward(x, step, cache))
         if self.feed_forward is not None:
             self._branch(stream, 2, self.feed_forward_norm, self.feed_forward.forward)
+
+
+@register_block("postnorm_residual")
+class PostNormResidualBlock(Block):
+    """h = norm1(alpha h + mixer(h)); h = norm2(alpha h + feed_forward(h)): the branches read the residual itself,
+    the norm comes after the sum (alpha is the norms' ``residual_mult``).  The residual is kept in float32 and, beside
+    it, in the compute dtype as ``stream.hidden``, the branches' input; a layer may have no feed-forward."""
+
+    graph_safe = True
+
+    def forward(self, stream: ResidualStream, step, cache) -> None:
+        if stream.hidden is None:    # the model's embedding left float32 rows only
+            stream.hidden = (stream.residual if stream.residual.dtype == self.mixer.ctx.dtype
+                             else stream.residual.to(self.mixer.ctx.dtype))
+        stream.delta = self.mixer.forward(stream.hidden, step, cache)
+        stream.delta_bias = self.mixer.output_bias
+        x = self.mixer_norm.forward(stream)
+        if self.feed_forward is not None:
+            stream.delta = self.feed_forward.forward(x)
+            self.feed_forward_norm.forward(stream)

@@ -46,3 +46,33 @@ class RMSNorm(Norm):
         if rows is None:
             stream.delta = None
         return out
+
+
+@register_norm("rmsnorm_after_sum")
+class RMSNormAfterSum(Norm):
+    """params: ``eps``, ``residual_mult`` (alpha), ``weight_name`` (default "weight").
+
+    The norm of a layer that normalises after the sum: x <- (alpha x + y + b) / sqrt(mean((alpha x + y + b)^2) + eps) * w,
+    where y is the pending branch output and b the bias that came with it.  The result replaces the float32 residual
+    and, rounded, ``stream.hidden``, which the next branch reads; the rounded rows are returned."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        self.eps = float(params["eps"])
+        self.alpha = float(params.get("residual_mult", 1.0))
+        self.weight = weights[params.get("weight_name", "weight")].to(torch.float32).contiguous()
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        return {params.get("weight_name", "weight"): TensorSpec((hidden_size,), "norm")}
+
+    def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None) -> torch.Tensor:
+        if rows is not None or not stream.plain:
+            raise ops.KernelError("rmsnorm_after_sum: the norm runs over all rows of one copy of the residual")
+        copy = stream.hidden if stream.hidden is not stream.residual else None
+        ops.scaled_add_rmsnorm(stream.residual, stream.delta, stream.delta_bias, None, self.alpha, self.weight,
+                               self.eps, copy)
+        stream.delta = stream.delta_bias = None
+        return stream.hidden
