@@ -22,6 +22,7 @@ from pathlib import Path
 # Random stand-in models by name: config.json contents of the architecture, sizes only.
 RANDOM_MODELS = {
     "givelix": dict(vocab_size=260),     # the Givelix design at a small size (``_givelix_stand_in``)
+    "fororax": dict(vocab_size=260),     # the Fororax design at a small size (``_fororax_stand_in``)
     # the reference's ModelConfig.tiny (src/llmserve/config.py:34-44) over the byte tokenizer's vocabulary
     "tiny": dict(vocab_size=260, hidden_size=128, intermediate_size=352, num_hidden_layers=4, num_attention_heads=4,
                  num_key_value_heads=2, max_position_embeddings=1024, rope_theta=10000.0, rms_norm_eps=1e-6),
@@ -46,8 +47,23 @@ def _givelix_stand_in(vocab_size: int) -> dict:
                        {"type": "latent_attention_2", "mixer": second, "mlp": mlp}]}
 
 
+def _fororax_stand_in(vocab_size: int) -> dict:
+    """A small model of the Fororax design: a layer with sink, head mixing and gate, a layer with the distance penalty,
+    a layer that reads the second layer's keys and values; mixtures of six experts and two identity experts."""
+    mlp = {"kind": "moe", "router": {"experts": 6, "identity": 2, "top": 2}, "expert": {"ff": 96, "limit": 1.0},
+           "shared": {"ff": 128, "limit": 2.0}}
+    heads = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 32 ** -0.5}
+    return {"architecture": "Fororax", "vocab": vocab_size, "width": 128, "max_positions": 1024, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "postln_alpha": 2.0, "logit_softcap": 30.0,
+            "layers": [{"type": "attention_2", "mixer": heads, "mlp": mlp},
+                       {"type": "attention", "mixer": heads, "mlp": mlp},
+                       {"type": "attention", "mixer": dict(heads, kv_from=1), "mlp": mlp}]}
+
+
 def tiny_config(vocab_size: int = 260, name: str = "tiny") -> dict:
     """config.json of a random stand-in model."""
+    if name == "fororax":
+        return _fororax_stand_in(vocab_size)
     if name == "givelix":
         return _givelix_stand_in(vocab_size)
     return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "attention_bias": True,

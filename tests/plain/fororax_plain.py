@@ -132,7 +132,7 @@ def route(x, router, correction, top: int):
 
 
 def mixture(x, w, prefix, mlp) -> torch.Tensor:
-    experts, identity, top = (int(mlp["router"][key]) for key in ("experts", "identity", "top"))
+    experts, identity, top = (int(mlp["router"].get(key, 0)) for key in ("experts", "identity", "top"))
     scores, chosen = route(x, w[prefix + "router"], w[prefix + "correction"], top)
     limit = float(mlp["expert"]["limit"])
     y = torch.zeros_like(x)
@@ -222,3 +222,103 @@ def load_folder(folder, round_to=None):
             tensor = tensor.to(torch.float64)
         weights[name] = tensor
     return cfg, weights
+
+
+# --------------------------------------------------------------------------- random models for the tests
+def tensor_shapes(cfg: dict) -> dict[str, tuple]:
+    """Every tensor of a model of this configuration, by name."""
+    width = int(cfg["width"])
+    shapes = {"embed": (int(cfg["vocab"]), width), "pos": (int(cfg["max_positions"]), width), "final.norm": (width,),
+              "head": (int(cfg["vocab"]), width)}
+    for index, layer in enumerate(cfg["layers"]):
+        m, p = layer["mixer"], f"l{index}."
+        heads, groups, dim, vdim = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        second = layer["type"] == "attention_2"
+        shapes[p + "norm1"] = (width,)
+        shapes[p + "mix.q"] = (heads * dim, width)
+        shapes[p + "mix.q.norm"] = (dim,)
+        shapes[p + "mix.o"] = (width, heads * vdim)
+        if m.get("kv_from") is None:
+            shapes[p + "mix.k"] = (groups * dim, width)
+            shapes[p + "mix.v"] = (groups * vdim, width)
+            shapes[p + "mix.k.norm"] = (dim,)
+        if second:
+            for name in ("q", "k", "v", "o"):
+                shapes[p + f"mix.{name}.b"] = (shapes[p + f"mix.{name}"][0],)
+            shapes[p + "mix.sink"] = (heads,)
+            shapes[p + "mix.talk"] = (heads, heads)
+            shapes[p + "mix.g"] = (heads * vdim, width)
+        else:
+            shapes[p + "mix.r1"] = (heads,)
+            shapes[p + "mix.r2"] = (heads,)
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            shapes[p + "norm2"] = (width,)
+            outputs = int(mlp["router"]["experts"]) + int(mlp["router"].get("identity", 0))
+            shapes[p + "mlp.router"] = (outputs, width)
+            shapes[p + "mlp.correction"] = (outputs,)
+            sized = [(f"e{j}.", int(mlp["expert"]["ff"])) for j in range(int(mlp["router"]["experts"]))]
+            if mlp.get("shared"):
+                sized.append(("shared.", int(mlp["shared"]["ff"])))
+                shapes[p + "mlp.shared.sg"] = (1, width)
+            for name, ff in sized:
+                shapes[p + "mlp." + name + "gate"] = (ff, width)
+                shapes[p + "mlp." + name + "up"] = (ff, width)
+                shapes[p + "mlp." + name + "down"] = (width, ff)
+    return shapes
+
+
+def random_weights(cfg: dict, seed: int) -> dict[str, torch.Tensor]:
+    """Random float32 weights with large gains, so that every mechanism moves the logits: peaked routers, clamps that
+    act, sinks and penalties of the size of the scores, a head table far from the identity."""
+    generator = torch.Generator().manual_seed(seed)
+
+    def normal(shape, std):
+        return torch.randn(shape, generator=generator) * std
+
+    def uniform(shape, lo, hi):
+        return lo + (hi - lo) * torch.rand(shape, generator=generator)
+
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.rsplit(".", 1)[-1]
+        if name == "embed":
+            tensor = normal(shape, 1.0)
+        elif name == "pos":
+            tensor = normal(shape, 0.5)
+        elif last in ("norm", "norm1", "norm2"):
+            tensor = uniform(shape, 0.6, 1.4)
+        elif last == "b":
+            tensor = normal(shape, 0.3)
+        elif last == "r1":
+            tensor = uniform(shape, 0.2, 1.5)
+        elif last == "r2":
+            tensor = uniform(shape, 0.05, 1.0)
+        elif last == "sink":
+            tensor = normal(shape, 1.5)
+        elif last == "talk":
+            tensor = 0.7 * torch.eye(shape[0]) + normal(shape, 0.3)
+        elif last == "correction":
+            tensor = normal(shape, 0.1)
+        elif last == "router":
+            tensor = normal(shape, 4.0 / shape[1] ** 0.5)
+        elif name == "head":
+            tensor = normal(shape, 3.0 / shape[1] ** 0.5)
+        elif last in ("gate", "up"):
+            tensor = normal(shape, 1.5 / shape[1] ** 0.5)
+        else:
+            tensor = normal(shape, 1.0 / shape[1] ** 0.5)
+        out[name] = tensor.to(torch.bfloat16).to(torch.float32).contiguous()   # values that bfloat16 holds exactly
+    return out
+
+
+def write_model(folder, cfg: dict, seed: int) -> dict[str, torch.Tensor]:
+    """config.json and model.safetensors (float32) of a random model; returns the weights."""
+    from safetensors.torch import save_file
+
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    weights = random_weights(cfg, seed)
+    (folder / "config.json").write_text(json.dumps(cfg, indent=1))
+    save_file(weights, str(folder / "model.safetensors"))
+    return weights
