@@ -19,6 +19,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "mma_common.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -27,52 +28,10 @@ LSE_CHECK_DEFINE(lse_check_attention_mma)
 
 namespace {
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
-  const int bytes = pred ? 16 : 0;  // 0: nothing is read, the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// Transpose of an 8 x 8 matrix of 16-bit values held one 32-bit register a thread (row = lane / 4, columns 2 (lane % 4), +1).
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-  uint32_t d;
-  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
-  return d;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 // Byte offset of 16-byte chunk `c` of row `r` in a [rows][D] bfloat16 tile whose
 // chunks are XOR-swizzled by the row, so that ldmatrix reads are conflict-free.
 template <int D> __device__ __forceinline__ uint32_t tile_off(int r, int c) {
   return (uint32_t)(r * (D * 2) + ((c ^ (r & 7)) << 4));
-}
-
-constexpr float LOG2E = 1.4426950408889634f;
-
-__device__ __forceinline__ float fast_exp2(float x) {   // 2^x, float32, 2^-inf = 0
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-  return y;
 }
 
 // Copies 16 consecutive keys (rows of D bfloat16, contiguous in one cache page) of K and of V
@@ -117,19 +76,6 @@ constexpr int DEC_STAGES = 3;
 constexpr int DEC_TILE = 16;
 constexpr int DEC_HEADS = 8;     // query heads of a group that a block takes: the N side of the instruction
 constexpr int BT_STAGE = 1024;   // block-table entries a block keeps in shared memory
-
-// page and offset of key j: by shift and mask when the page size is a power of two
-struct PageMath {
-  int size, shift;
-  __device__ __forceinline__ explicit PageMath(int page_size) : size(page_size), shift(-1) {
-    if ((page_size & (page_size - 1)) == 0) {
-      shift = 0;
-      while ((1 << shift) < page_size) ++shift;
-    }
-  }
-  __device__ __forceinline__ int page(int j) const { return shift >= 0 ? j >> shift : j / size; }
-  __device__ __forceinline__ int offset(int j) const { return shift >= 0 ? j & (size - 1) : j % size; }
-};
 
 // CLUSTER: the splits of one (row, kv head) are the blocks of a thread-block cluster and add
 // themselves up through distributed shared memory; else through global partial sums and a counter.

@@ -368,6 +368,26 @@ extern "C" int lse_attention_scored(const void* q, const void* k_cache, const vo
   return LSE_ERR_BAD_ARGUMENT;
 }
 
+// The second half of a launch with partials, for kernels of other files that leave partials in the same layout
+// ([t][head][value slot][chunk][dv + 2]: sums, maximum, total): out [T, n_q, n_values, dv] in bfloat16 or float32.
+extern "C" int lse_attention_scored_merge(const float* partials, void* out, int out_dtype, const int* segment_of_token,
+                                          const int* positions, const float* sink, int tokens, int n_q, int n_values,
+                                          int dv, int max_chunks, int num_segments, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (dv <= 0 || dv > MAX_D || n_q * n_values > 65535 || max_chunks <= 0) return LSE_ERR_BAD_ARGUMENT;
+  const dim3 grid(tokens, n_q * n_values);
+  const int threads = ((dv + 31) / 32) * 32;
+  if (out_dtype == LSE_DTYPE_F32)
+    lse_launch(attention_scored_merge_kernel<float>, grid, threads, 0, stream, partials, (float*)out, segment_of_token,
+               positions, sink, n_values, dv, max_chunks, num_segments);
+  else if (out_dtype == LSE_DTYPE_BF16)
+    lse_launch(attention_scored_merge_kernel<__nv_bfloat16>, grid, threads, 0, stream, partials, (__nv_bfloat16*)out,
+               segment_of_token, positions, sink, n_values, dv, max_chunks, num_segments);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
+}
+
 // wide float32 [T, n_q, n_values, dv] (n_values = n_kv when cross, else 1); mix float32 [n_q, n_q] or null;
 // gate_proj [T, ld] (columns from the pointer on) or a float32 stack of partial sums, or null; out [T, n_q * dv].
 extern "C" int lse_head_mix_gate(const float* wide, const float* mix, const void* gate_proj, int gate_dtype,

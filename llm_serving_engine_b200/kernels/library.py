@@ -92,6 +92,12 @@ _SIGNATURES = {
     "lse_attention_scored": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                              c_int, c_int, c_void_p, c_int, c_void_p],
+    "lse_attention_scored_merge": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_void_p],
+    "lse_attention_scored_mma_supported": [c_int, c_int, c_int, c_int],
+    "lse_attention_scored_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                 c_int, c_void_p, c_int, c_void_p],
     "lse_head_mix_gate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
@@ -135,7 +141,8 @@ def register_signatures(signatures: dict) -> None:
 
 CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc",
                  "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_attention_latent",
-                 "lse_check_attention_latent_mma", "lse_check_rowwise_postnorm", "lse_check_attention_scored")
+                 "lse_check_attention_latent_mma", "lse_check_rowwise_postnorm", "lse_check_attention_scored",
+                 "lse_check_attention_scored_mma")
 CHECK_KINDS = {1: "token id", 2: "cache slot", 3: "block-table entry", 4: "segment number", 5: "row index"}
 
 

@@ -820,13 +820,17 @@ def head_norm_kv_write(proj: torch.Tensor, bias: torch.Tensor | None, q_norm: to
 def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                      block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
                      r1: torch.Tensor | None = None, r2: torch.Tensor | None = None, sink: torch.Tensor | None = None,
-                     cross: bool = False, split: bool | None = None) -> torch.Tensor:
+                     cross: bool = False, split: bool | None = None, segment_start: torch.Tensor | None = None,
+                     segment_first_position: torch.Tensor | None = None, tensor_cores: bool = True) -> torch.Tensor:
     """Causal attention of every row of the step over its request's pages, with the scores or weights changed:
     s_ij = q_i . k_j * scale - r1_h ln(1 + r2_h (i - j)) (``r1``, ``r2`` float32 [n_q]); exp(sink_h) in the
     denominator (``sink`` float32 [n_q]).  q [T, n_q, dk]; k_cache [pages, n_kv, page, dk]; v_cache [.., dv];
     out [T, n_q, dv], or with ``cross`` [T, n_q, n_kv, dv]: head h's weights applied to the values of every
-    key/value head.  ``out`` is in the cache's dtype or float32.  ``split`` as for :func:`paged_attention_generic`."""
-    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions, r1, r2, sink)
+    key/value head.  ``out`` is in the cache's dtype or float32.  ``split`` as for :func:`paged_attention_generic`.
+    Given the step's ``segment_start`` (int32 [S + 1]) and ``segment_first_position`` (int32 [S]), bfloat16 shapes that
+    the tensor-core kernel takes run there (``tensor_cores=False``: the general kernel, for comparisons)."""
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions, r1, r2, sink, segment_start,
+               segment_first_position)
     tokens, n_q, dk = q.shape
     n_kv, page_size, dv = k_cache.shape[1], k_cache.shape[2], v_cache.shape[3]
     n_values = n_kv if cross else 1
@@ -846,6 +850,22 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         chunk = int(lib.lse_attention_scored_chunk())
         max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
         partials = torch.empty(tokens * n_q * n_values * max_chunks * (dv + 2), dtype=torch.float32, device=q.device)
+    if (tensor_cores and segment_start is not None and segment_first_position is not None
+            and attention_scored_mma_supported(dk, dv, n_q, n_kv, q.dtype)):
+        segments = segment_first_position.shape[0]
+        assert segment_start.dtype == torch.int32 and segment_start.shape[0] == segments + 1 and segments == block_tables.shape[0]
+        check(lib.lse_attention_scored_mma(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                           int(out.dtype == torch.float32), block_tables.data_ptr(), block_tables.stride(0),
+                                           segment_start.data_ptr(), segment_first_position.data_ptr(), segments, _ptr(r1),
+                                           _ptr(r2), _ptr(sink), tokens, n_q, n_kv, dk, dv, int(cross), page_size,
+                                           float(scale), k_cache.shape[0], _ptr(partials), max_chunks, _stream()),
+              "attention_scored_mma")
+        if partials is not None:
+            check(lib.lse_attention_scored_merge(partials.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                                                 segment_of_token.data_ptr(), positions.data_ptr(), _ptr(sink), tokens, n_q,
+                                                 n_values, dv, max_chunks, block_tables.shape[0], _stream()),
+                  "attention_scored_merge")
+        return out
     check(lib.lse_attention_scored(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
                                    int(out.dtype == torch.float32 and q.dtype != torch.float32), block_tables.data_ptr(),
                                    block_tables.stride(0), segment_of_token.data_ptr(), positions.data_ptr(), _ptr(r1),
@@ -853,6 +873,14 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                                    k_cache.shape[0], block_tables.shape[0], _ptr(partials), max_chunks, _stream()),
           "attention_scored")
     return out
+
+
+def attention_scored_mma_supported(dk: int, dv: int, n_q: int, n_kv: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core form of :func:`attention_scored` takes this shape (bfloat16; keys and values of one
+    size, 32, 48, 64, 96 or 128; at most 64 query heads a group)."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(library.load().lse_attention_scored_mma_supported(int(dk), int(dv), int(n_q), int(n_kv)))
 
 
 def head_mix_gate(wide: torch.Tensor, mix: torch.Tensor | None, gate_proj: torch.Tensor | None, gate_offset: int,

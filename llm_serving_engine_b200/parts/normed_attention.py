@@ -28,6 +28,10 @@ class NormedAttention(Mixer):
     and ``tensor_names``.  Queries and keys are RMS-normed per head with one weight [dim] shared by the heads; there
     is no rotation: positions enter through the distance penalty or not at all.
 
+    Shapes that the tensor-core kernel takes (bfloat16, keys and values of one size that is 32, 48, 64, 96 or 128) run
+    there, prompt portions as tiles of rows and few rows with their keys split into chunks; the rest, and float32, on
+    the general kernel.
+
     One stacked product gives [q | k | v | gate]; one kernel norms the heads, adds the biases and writes keys and
     values into the pages; the attention kernel applies penalty and sink; with mixing it leaves head g's weights
     applied to every key/value head's values in float32, and a small kernel takes the mixed sums and the gate."""
@@ -107,12 +111,14 @@ class NormedAttention(Mixer):
         attended = torch.empty((tokens, self.n_q * self.dv), dtype=x.dtype, device=x.device)
         if self.mix is None and self.gate_offset < 0:
             ops.attention_scored(q, cache.keys, cache.values, attended.view(tokens, self.n_q, self.dv), cache.block_tables,
-                                 step.segment_of_token, step.positions, self.scale, self.r1, self.r2, self.sink)
+                                 step.segment_of_token, step.positions, self.scale, self.r1, self.r2, self.sink,
+                                 segment_start=step.segment_start, segment_first_position=step.segment_first_position)
         else:
             cross = self.mix is not None and self.n_kv > 1
             wide = torch.empty((tokens, self.n_q, self.n_kv if cross else 1, self.dv), dtype=torch.float32, device=x.device)
             ops.attention_scored(q, cache.keys, cache.values, wide, cache.block_tables, step.segment_of_token,
-                                 step.positions, self.scale, self.r1, self.r2, self.sink, cross=cross)
+                                 step.positions, self.scale, self.r1, self.r2, self.sink, cross=cross,
+                                 segment_start=step.segment_start, segment_first_position=step.segment_first_position)
             gate_bias = None
             if self.gate_offset >= 0 and self.in_bias is not None and self.in_bias.shape[0] > self.gate_offset:
                 gate_bias = self.in_bias[self.gate_offset:]

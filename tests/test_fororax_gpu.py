@@ -471,3 +471,52 @@ def test_router_choice_uses_the_correction_and_the_weights_do_not():
     assert float((weights.cpu() - dense[:, :outputs - identity]).abs().max()) <= 1e-6
     assert float((identity_weight.cpu() - dense[:, outputs - identity:].sum(-1)).abs().max()) <= 1e-6
     assert float((shared_gate.cpu() - torch.sigmoid(x.double() @ gate_w.double())).abs().max()) <= 1e-6
+
+
+def test_tensor_core_attention_against_the_general_kernel():
+    """Portions of several requests beside single tokens, pages scattered, groups of one, three (which does not divide a
+    tile's 64 rows), eight and nine heads, with the penalty, the sink and the values of every group, whole and split
+    by chunks: the tensor-core kernel against the float32-arithmetic kernel on the same bfloat16 inputs, and one far
+    key that must be found."""
+    from llm_serving_engine_b200.kernels import ops
+    import numpy as np
+
+    torch.manual_seed(8)
+    page = 16
+    for heads, groups, size in ((4, 2, 48), (3, 1, 32), (8, 8, 64), (16, 2, 128), (18, 2, 96), (4, 2, 64)):
+        counts, firsts = [70, 1, 33, 1, 5], [300, 519, 0, 0, 63]
+        contexts = [first + count for first, count in zip(firsts, counts)]
+        pages_each = [-(-context // page) for context in contexts]
+        pool_pages = sum(pages_each) + 3
+        k_cache = (torch.randn(pool_pages, groups, page, size) * 0.5).to(torch.bfloat16).cuda()
+        v_cache = torch.randn(pool_pages, groups, page, size).to(torch.bfloat16).cuda()
+        order = torch.randperm(pool_pages).to(torch.int32)
+        table = torch.full((len(counts), max(pages_each)), -1, dtype=torch.int32)
+        cursor = 0
+        for index, count in enumerate(pages_each):
+            table[index, :count] = order[cursor:cursor + count]
+            cursor += count
+        total = sum(counts)
+        q = (torch.randn(total, heads, size) * 0.5).to(torch.bfloat16)
+        k_cache[int(table[0, 1]), groups - 1, 3] = (q[5, heads - 1] * 4.0).cuda()     # key 19 of request 0 stands out for the last head
+        starts = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32).cuda()
+        seg = torch.cat([torch.full((count,), index, dtype=torch.int32) for index, count in enumerate(counts)]).cuda()
+        pos = torch.cat([torch.arange(first, first + count, dtype=torch.int32) for first, count in zip(firsts, counts)]).cuda()
+        first_pos = torch.tensor(firsts, dtype=torch.int32).cuda()
+        assert ops.attention_scored_mma_supported(size, size, heads, groups, torch.bfloat16)
+        assert not ops.attention_scored_mma_supported(size, size + 16, heads, groups, torch.bfloat16)
+        sink = torch.linspace(-1.0, 2.0, heads).cuda()
+        r1, r2 = (torch.rand(heads) * 0.2).cuda(), (torch.rand(heads) * 0.5 + 0.01).cuda()
+        for kind in ("plain", "penalty", "sink", "sink_cross"):
+            extra = {"penalty": dict(r1=r1, r2=r2), "sink": dict(sink=sink), "sink_cross": dict(sink=sink, cross=True)}.get(kind, {})
+            slots = groups if kind == "sink_cross" else 1
+            for split in (False, True):
+                for out_dtype in (torch.bfloat16, torch.float32):
+                    want = torch.empty(total, heads, slots, size, dtype=out_dtype, device="cuda")
+                    got = torch.full_like(want, float("nan"))
+                    ops.attention_scored(q.cuda(), k_cache, v_cache, want, table.cuda(), seg, pos, 0.3, split=split,
+                                         tensor_cores=False, **extra)
+                    ops.attention_scored(q.cuda(), k_cache, v_cache, got, table.cuda(), seg, pos, 0.3, split=split,
+                                         segment_start=starts, segment_first_position=first_pos, **extra)
+                    error = float((got.float() - want.float()).abs().max())
+                    assert error <= 2e-2 * max(1.0, float(want.float().abs().max())), (heads, groups, size, kind, split, error)
