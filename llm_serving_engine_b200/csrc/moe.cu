@@ -7,11 +7,18 @@
 // was not chosen), the sum of the chosen identity experts' weights, and the gate of the shared expert,
 // sigmoid(w_sg . x).
 //
-// Activation (experts side by side in one product): the row of `gate_up` is [gate (I values) | up (I values)], where
-// the I columns are `experts` blocks of `ff` columns followed by `shared_ff` columns of the shared expert:
+// Activation (experts side by side in one product): the row of `gate_up` holds, expert by expert, [gate (ff values) |
+// up (ff values)], then [gate | up] of the shared expert (shared_ff values each); the output row holds the experts'
+// ff columns side by side, then the shared expert's:
 //   g = min(gate, limit);  u = clamp(up, -limit, limit);  out = c * g * sigmoid(1.702 g) * (u + 1)
-// with c the token's weight of the column's expert (the shared gate for the shared columns).  The down product over
-// all I columns then is the weighted sum over the experts.
+// with c the token's weight of the column's expert (the shared gate for the shared columns; 1 without weights).  The
+// down product over all columns then is the weighted sum over the experts.
+//
+// Rows grouped by expert (many rows): every (token, chosen real expert) pair gets a row of its own in a buffer in
+// which the rows of one expert are consecutive; `lse_moe_group_rows` counts, scans and places them (one block; the
+// order inside an expert's range is not fixed, a row's result does not depend on it), `lse_moe_gather_rows` copies the
+// tokens' inputs there, a grouped product runs per expert over its range, and `lse_moe_combine` adds, per token, its
+// rows times their weights in the order of its choices, and the identity experts' share of the input.
 #include "common.cuh"
 
 namespace {
@@ -94,20 +101,90 @@ __global__ void moe_gated_act_kernel(const TI* __restrict__ gate_up, int n_parti
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= inter) return;
   const bool shared = i >= experts * ff;
-  const float c = shared ? (shared_gate ? shared_gate[t] : 1.f) : expert_weights[(size_t)t * experts + i / ff];
+  const float c = shared ? (shared_gate ? shared_gate[t] : 1.f)
+                         : (expert_weights ? expert_weights[(size_t)t * experts + i / ff] : 1.f);
   TO* dst = out + (size_t)t * inter + i;
   if (c == 0.f) { *dst = from_f32<TO>(0.f); return; }   // an expert that the token did not choose
   const TI* row = gate_up + (size_t)t * 2 * inter;
+  const int gate_at = shared ? 2 * experts * ff + (i - experts * ff) : (i / ff) * 2 * ff + i % ff;
+  const int up_at = gate_at + (shared ? shared_ff : ff);
   float g = 0.f, u = 0.f;
   for (int p = 0; p < n_partials; ++p) {
-    g += to_f32<TI>(row[(size_t)p * partial_stride + i]);
-    u += to_f32<TI>(row[(size_t)p * partial_stride + inter + i]);
+    g += to_f32<TI>(row[(size_t)p * partial_stride + gate_at]);
+    u += to_f32<TI>(row[(size_t)p * partial_stride + up_at]);
   }
   const float lim = shared ? shared_limit : limit;
   g = fminf(g, lim);
   u = fminf(fmaxf(u, -lim), lim);
   const float act = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
   *dst = from_f32<TO>(c * act);
+}
+// One block: counts[e] = rows of expert e, offsets (inclusive sums, what a grouped product takes), and for every
+// (token, choice) its row in the grouped buffer (-1: an identity expert, or padding).
+__global__ void __launch_bounds__(1024)
+moe_group_rows_kernel(const int* __restrict__ chosen, const int* __restrict__ segment_of_token, int* __restrict__ row_of,
+                      int* __restrict__ offsets, int tokens, int top, int experts) {
+  extern __shared__ int group_smem[];   // [experts] counts, then [experts] first rows
+  pdl_launch_dependents();
+  pdl_wait();
+  int* count = group_smem;
+  int* first = group_smem + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  const int entries = tokens * top;
+  for (int i = threadIdx.x; i < entries; i += blockDim.x) {
+    const int e = chosen[i];
+    const bool real = e >= 0 && e < experts && (!segment_of_token || segment_of_token[i / top] >= 0);
+    row_of[i] = real ? atomicAdd(&count[e], 1) : -1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int running = 0;
+    for (int e = 0; e < experts; ++e) { first[e] = running; running += count[e]; offsets[e] = running; }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < entries; i += blockDim.x)
+    if (row_of[i] >= 0) row_of[i] += first[chosen[i]];
+}
+
+template <typename T>
+__global__ void moe_gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_of, T* __restrict__ grouped,
+                                       int width, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int row = row_of[blockIdx.x];    // blockIdx.x = token * top + choice
+  if (row < 0) return;
+  const T* src = x + (size_t)(blockIdx.x / top) * width;
+  T* dst = grouped + (size_t)row * width;
+  if (sizeof(T) == 2 && width % 8 == 0) {
+    for (int i = threadIdx.x; i < width / 8; i += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// y[t] (+)= sum_k w[t, chosen[t, k]] * down[row_of[t, k]] + identity_weight[t] * x[t]   (accumulate: y holds the
+// shared expert's output already; else it is overwritten)
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ down, const int* __restrict__ row_of, const int* __restrict__ chosen,
+                                   const float* __restrict__ expert_weights, const float* __restrict__ identity_weight,
+                                   const T* __restrict__ x, float* __restrict__ y, int width, int top, int experts,
+                                   int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float identity = identity_weight ? identity_weight[t] : 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float sum = accumulate ? y[(size_t)t * width + i] : 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int row = row_of[t * top + k];
+      if (row >= 0)
+        sum = fmaf(expert_weights[(size_t)t * experts + chosen[t * top + k]], to_f32<T>(down[(size_t)row * width + i]), sum);
+    }
+    if (identity != 0.f) sum = fmaf(identity, to_f32<T>(x[(size_t)t * width + i]), sum);
+    y[(size_t)t * width + i] = sum;
+  }
 }
 }  // namespace
 
@@ -151,5 +228,47 @@ extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partia
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_MOE_ACT_CASE(float, __nv_bfloat16);
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_MOE_ACT_CASE
+  LSE_LAUNCH_CHECK();
+}
+
+// chosen int32 [tokens, top] (what lse_moe_route left); row_of int32 [tokens, top]; offsets int32 [experts].
+extern "C" int lse_moe_group_rows(const int* chosen, const int* segment_of_token, int* row_of, int* offsets, int tokens,
+                                  int top, int experts, cudaStream_t stream) {
+  if (tokens <= 0 || experts <= 0) return 0;
+  if (top <= 0) return LSE_ERR_BAD_ARGUMENT;
+  if (experts > 4096) return LSE_ERR_TOO_LARGE;
+  lse_launch(moe_group_rows_kernel, 1, 1024, sizeof(int) * 2 * (size_t)experts, stream, chosen, segment_of_token, row_of,
+             offsets, tokens, top, experts);
+  LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_moe_gather_rows(const void* x, int dtype, const int* row_of, void* grouped, int tokens, int top,
+                                   int width, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (top <= 0) return LSE_ERR_BAD_ARGUMENT;
+  if (dtype == LSE_DTYPE_F32)
+    lse_launch(moe_gather_rows_kernel<float>, (unsigned)tokens * top, 128, 0, stream, (const float*)x, row_of,
+               (float*)grouped, width, top);
+  else if (dtype == LSE_DTYPE_BF16)
+    lse_launch(moe_gather_rows_kernel<__nv_bfloat16>, (unsigned)tokens * top, 128, 0, stream,
+               (const __nv_bfloat16*)x, row_of, (__nv_bfloat16*)grouped, width, top);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_moe_combine(const void* down, int dtype, const int* row_of, const int* chosen, const float* expert_weights,
+                               const float* identity_weight, const void* x, float* y, int tokens, int width, int top,
+                               int experts, int accumulate, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == LSE_DTYPE_F32)
+    lse_launch(moe_combine_kernel<float>, tokens, threads, 0, stream, (const float*)down, row_of, chosen, expert_weights,
+               identity_weight, (const float*)x, y, width, top, experts, accumulate);
+  else if (dtype == LSE_DTYPE_BF16)
+    lse_launch(moe_combine_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)down, row_of, chosen,
+               expert_weights, identity_weight, (const __nv_bfloat16*)x, y, width, top, experts, accumulate);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
 }

@@ -88,6 +88,10 @@ _SIGNATURES = {
                       c_int, c_int, c_int, c_int, c_void_p],
     "lse_moe_gated_act": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_float, c_void_p],
+    "lse_moe_group_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_moe_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_int, c_int, c_void_p],
     "lse_attention_scored_chunk": [],
     "lse_attention_scored": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,

@@ -936,15 +936,58 @@ def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_ga
                   out: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float) -> torch.Tensor:
     """out[t, i] = c * g * sigmoid(1.702 g) * (u + 1) with g = min(gate_i, limit), u = clamp(up_i, -limit, limit), over
     the columns of all experts side by side (``experts`` blocks of ``ff``, then ``shared_ff`` of the shared expert with
-    its own limit); c is the token's weight of the column's expert (``shared_gate`` for the shared columns).
-    ``gate_up`` is [T, 2 I] (the row is [gate | up]) or a float32 stack of partial sums."""
+    its own limit); c is the token's weight of the column's expert (``shared_gate`` for the shared columns; 1 where
+    the weights are None).  ``gate_up`` is [T, 2 I] (expert by expert [gate | up], then the shared expert's
+    [gate | up]) or a float32 stack of partial sums."""
     _need_cuda(gate_up, expert_weights, shared_gate, out)
     tokens, inter = out.shape
     assert inter == experts * ff + shared_ff and out.is_contiguous() and gate_up.shape[-1] == 2 * inter
     gate_up, n_partials, stride = _partials(gate_up, tokens, 2 * inter)
-    assert expert_weights.dtype == torch.float32 and expert_weights.shape == (tokens, experts) and expert_weights.is_contiguous()
+    assert expert_weights is None or (expert_weights.dtype == torch.float32 and expert_weights.shape == (tokens, experts)
+                                      and expert_weights.is_contiguous())
     check(library.load().lse_moe_gated_act(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride,
-                                           expert_weights.data_ptr(), _ptr(shared_gate), out.data_ptr(),
+                                           _ptr(expert_weights), _ptr(shared_gate), out.data_ptr(),
                                            dtype_code(out.dtype), tokens, experts, ff, shared_ff, float(limit),
                                            float(shared_limit), _stream()), "moe_gated_act")
     return out
+
+
+def moe_group_rows(chosen: torch.Tensor, experts: int, segment_of_token: torch.Tensor | None = None):
+    """Places for the rows of a grouped product: ``chosen`` int32 [T, top] (a router's choices; ids from ``experts`` on
+    are identity experts and get no row).  Returns (row_of int32 [T, top]: the row of every (token, choice), -1 for
+    none; offsets int32 [experts]: the end of every expert's range of rows).  Rows of padding tokens
+    (``segment_of_token`` < 0) get no place."""
+    _need_cuda(chosen, segment_of_token)
+    tokens, top = chosen.shape
+    assert chosen.dtype == torch.int32 and chosen.is_contiguous()
+    row_of = torch.empty_like(chosen)
+    offsets = torch.empty((experts,), dtype=torch.int32, device=chosen.device)
+    check(library.load().lse_moe_group_rows(chosen.data_ptr(), _ptr(segment_of_token), row_of.data_ptr(), offsets.data_ptr(),
+                                            tokens, top, int(experts), _stream()), "moe_group_rows")
+    return row_of, offsets
+
+
+def moe_gather_rows(x: torch.Tensor, row_of: torch.Tensor, grouped: torch.Tensor) -> torch.Tensor:
+    """grouped[row_of[t, k]] = x[t] for every place that is not -1."""
+    _need_cuda(x, row_of, grouped)
+    tokens, top = row_of.shape
+    assert x.is_contiguous() and grouped.is_contiguous() and x.dtype == grouped.dtype and x.shape[1] == grouped.shape[1]
+    assert grouped.shape[0] >= tokens * top and x.shape[0] == tokens
+    check(library.load().lse_moe_gather_rows(x.data_ptr(), dtype_code(x.dtype), row_of.data_ptr(), grouped.data_ptr(),
+                                             tokens, top, x.shape[1], _stream()), "moe_gather_rows")
+    return grouped
+
+
+def moe_combine(down: torch.Tensor, row_of: torch.Tensor, chosen: torch.Tensor, expert_weights: torch.Tensor,
+                identity_weight: torch.Tensor | None, x: torch.Tensor, y: torch.Tensor, accumulate: bool) -> torch.Tensor:
+    """y[t] (+)= sum_k expert_weights[t, chosen[t, k]] * down[row_of[t, k]] + identity_weight[t] * x[t], the sum in the
+    order of the token's choices; y float32 [T, W] (``accumulate``: it holds something already, else it is overwritten)."""
+    _need_cuda(down, row_of, chosen, expert_weights, identity_weight, x, y)
+    tokens, top = row_of.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == x.shape and x.is_contiguous() and down.is_contiguous()
+    assert down.dtype == x.dtype and down.shape[1] == x.shape[1] and expert_weights.is_contiguous()
+    check(library.load().lse_moe_combine(down.data_ptr(), dtype_code(down.dtype), row_of.data_ptr(), chosen.data_ptr(),
+                                         expert_weights.data_ptr(), _ptr(identity_weight), x.data_ptr(), y.data_ptr(),
+                                         tokens, x.shape[1], top, expert_weights.shape[1], int(accumulate), _stream()),
+          "moe_combine")
+    return y

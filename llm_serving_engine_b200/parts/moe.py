@@ -2,12 +2,18 @@
 gated shared expert."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import FeedForward, register_feed_forward
 from .linear import linear, linear_partials, SKINNY_MAX_ROWS
+
+# Rows of a step from which the rows are grouped by expert (bfloat16).  Below it every expert's product is taken for
+# every row: with few rows the experts' weights are what the step waits for, and nearly all of them are read either way.
+GROUPED_FROM_ROWS = int(os.environ.get("LSE_MOE_GROUPED_FROM", "128"))
 
 _DEFAULT_NAMES = {"router": "router", "correction": "correction", "expert": "e{index}.", "shared": "shared.",
                   "gate": "gate", "up": "up", "down": "down", "shared_gate": "sg"}
@@ -24,11 +30,16 @@ class ClampedMoE(FeedForward):
     Router: s = softmax(W_router x) over all outputs, in float32; the ``top`` outputs with the largest s + correction
     are chosen; the weights are their s, not renormalised.
 
-    All experts run side by side as two products: [all gates | all ups] of every expert and the shared one stacked into
-    one matrix, the activation kernel multiplying each expert's columns by the token's weight for it (zero where it
-    was not chosen), and the down matrices side by side, so that the second product is the weighted sum over the
-    experts.  Which kernels run does not depend on the routing (the step can be replayed from a CUDA graph); the price
-    is that every expert's product is taken for every token."""
+    The experts' matrices are held once, stacked: [gate; up] expert by expert and then of the shared expert as one
+    matrix, and the down matrices side by side as another.  Two ways through them, chosen by the number of rows and the
+    precision only (neither depends on the routing, so a step can be replayed from a CUDA graph):
+
+    * few rows (decoding) and float32: all experts side by side as two products; the activation kernel multiplies each
+      expert's columns by the token's weight for it (zero where it was not chosen), so that the second product is the
+      weighted sum over the experts.  With a handful of tokens nearly every expert's weights are read anyway.
+    * many bfloat16 rows: every (token, chosen expert) pair gets a row in a buffer grouped by expert (two small
+      kernels), the library's grouped product runs over views of the same stacked matrices, and a kernel adds each
+      token's rows times their weights in float32, with the identity experts' share, onto the shared expert's output."""
 
     graph_safe = True
 
@@ -44,14 +55,21 @@ class ClampedMoE(FeedForward):
         prefixes = [names["expert"].format(index=index) for index in range(self.experts)]
         if shared:
             prefixes.append(names["shared"])
-        gates = [weights[prefix + names["gate"]] for prefix in prefixes]
-        ups = [weights[prefix + names["up"]] for prefix in prefixes]
+        pairs = [weights[prefix + names[which]] for prefix in prefixes for which in ("gate", "up")]
         self.inter = self.experts * self.ff + self.shared_ff
-        self.gate_up_weight = torch.cat(gates + ups, dim=0).contiguous() if prefixes else None
+        self.gate_up_weight = torch.cat(pairs, dim=0).contiguous() if prefixes else None
         self.down_weight = torch.cat([weights[prefix + names["down"]] for prefix in prefixes], dim=1).contiguous() if prefixes else None
         self.router = weights[names["router"]].contiguous()
         self.correction = weights[names["correction"]].float().contiguous() if p.get("correction", True) else None
         self.shared_gate_w = weights[names["shared"] + names["shared_gate"]].reshape(-1).contiguous() if shared else None
+        # views of the stacked matrices for the grouped product: [experts, width, 2 ff] and [experts, ff, width]
+        self._grouped_gate_up = self._grouped_down = None
+        width = self.router.shape[1]
+        if (self.experts and self.gate_up_weight.dtype == torch.bfloat16 and width % 8 == 0 and self.ff % 8 == 0
+                and self.inter % 8 == 0 and hasattr(torch, "_grouped_mm")):
+            routed = self.experts * self.ff
+            self._grouped_gate_up = self.gate_up_weight[:2 * routed].view(self.experts, 2 * self.ff, width).transpose(1, 2)
+            self._grouped_down = self.down_weight.as_strided((self.experts, self.ff, width), (self.ff, 1, self.inter))
 
     @classmethod
     def expected_tensors(cls, params, hidden_size):
@@ -71,8 +89,35 @@ class ClampedMoE(FeedForward):
             out[prefix + names["down"]] = TensorSpec((hidden_size, width))
         return out
 
+    def _grouped(self, x):
+        """Rows grouped by expert (see the class)."""
+        tokens, width = x.shape
+        chosen = torch.empty((tokens, self.top), dtype=torch.int32, device=x.device)
+        expert_weights, identity_weight, shared_gate = ops.moe_route(x, self.router, self.correction, self.shared_gate_w,
+                                                                     self.identity, self.top, chosen)
+        y = None
+        if self.shared_ff:   # the shared expert: two plain products, its gate folded into the activation
+            routed = self.experts * self.ff
+            gate_up = linear(x, self.gate_up_weight[2 * routed:])
+            act = torch.empty((tokens, self.shared_ff), dtype=x.dtype, device=x.device)
+            ops.moe_gated_act(gate_up, None, shared_gate, act, 0, 1, self.shared_ff, self.limit, self.shared_limit)
+            y = linear(act, self.down_weight[:, routed:], out_dtype=torch.float32)
+        row_of, offsets = ops.moe_group_rows(chosen, self.experts)
+        rows = tokens * self.top
+        grouped = torch.empty((rows, width), dtype=x.dtype, device=x.device)
+        ops.moe_gather_rows(x, row_of, grouped)
+        gate_up = torch._grouped_mm(grouped, self._grouped_gate_up, offs=offsets)     # rows beyond the last range stay as they are
+        act = torch.empty((rows, self.ff), dtype=x.dtype, device=x.device)
+        ops.moe_gated_act(gate_up, None, None, act, 1, self.ff, 0, self.limit, 0.0)
+        down = torch._grouped_mm(act, self._grouped_down, offs=offsets)
+        out = y if y is not None else torch.empty((tokens, width), dtype=torch.float32, device=x.device)
+        return ops.moe_combine(down, row_of, chosen, expert_weights, identity_weight if self.identity else None, x, out,
+                               accumulate=y is not None)
+
     def forward(self, x):
         tokens = x.shape[0]
+        if self._grouped_gate_up is not None and x.dtype == torch.bfloat16 and tokens >= GROUPED_FROM_ROWS:
+            return self._grouped(x)
         expert_weights, identity_weight, shared_gate = ops.moe_route(x, self.router, self.correction, self.shared_gate_w,
                                                                      self.identity, self.top)
         if self.inter:

@@ -520,3 +520,47 @@ def test_tensor_core_attention_against_the_general_kernel():
                                          segment_start=starts, segment_first_position=first_pos, **extra)
                     error = float((got.float() - want.float()).abs().max())
                     assert error <= 2e-2 * max(1.0, float(want.float().abs().max())), (heads, groups, size, kind, split, error)
+
+
+@pytest.mark.parametrize("rows", [5, 70, 300])
+def test_mixture_of_experts_in_bfloat16_both_ways_through_the_experts(rows, monkeypatch):
+    """bfloat16: few rows take every expert's product (partial sums), many rows are grouped by expert for the grouped
+    product; both against the plain mixture, and the two ways against each other on the same rows.  One case has an
+    expert that no row chooses and rows whose choices are all identity experts."""
+    from llm_serving_engine_b200.parts import moe as moe_part
+
+    for case, (experts, identity, top, ff, limit, shared, width) in enumerate((
+            (5, 2, 3, 40, 0.8, (56, 1.5), 72), (4, 0, 1, 24, 0.5, None, 64), (2, 6, 2, 16, 0.3, (8, 0.5), 104),
+            (12, 4, 3, 64, 1.0, (96, 2.0), 128))):
+        got, want, *_ = _mixture_case(experts, identity, top, ff, limit, shared, width, rows, seed=10 * rows + case,
+                                      dtype=torch.bfloat16)
+        scale = float(want.abs().max())
+        assert float((got - want).abs().max()) <= 3e-2 * scale, (rows, case)
+        monkeypatch.setattr(moe_part, "GROUPED_FROM_ROWS", 1 if rows < moe_part.GROUPED_FROM_ROWS else 10 ** 9)
+        other, *_ = _mixture_case(experts, identity, top, ff, limit, shared, width, rows, seed=10 * rows + case,
+                                  dtype=torch.bfloat16)
+        monkeypatch.undo()
+        assert float((got - other).abs().max()) <= 3e-2 * scale, (rows, case, "the two ways")
+
+
+def test_rows_grouped_by_expert_have_places_of_their_own():
+    from llm_serving_engine_b200.kernels import ops
+
+    torch.manual_seed(9)
+    tokens, top, experts = 333, 3, 7
+    chosen = torch.stack([torch.randperm(experts + 2)[:top] for _ in range(tokens)]).to(torch.int32)   # ids 7, 8: identity
+    chosen[:, 0][chosen[:, 0] == 4] = 5                                                               # expert 4 is rarer
+    segment = torch.zeros(tokens, dtype=torch.int32)
+    segment[-5:] = -1                                                                                 # padding rows
+    row_of, offsets = ops.moe_group_rows(chosen.cuda(), experts, segment.cuda())
+    row_of, offsets = row_of.cpu(), offsets.cpu()
+    live = chosen[:-5]
+    counts = torch.tensor([(live == e).sum() for e in range(experts)])
+    assert torch.equal(offsets.long(), counts.cumsum(0))
+    assert bool((row_of[-5:] == -1).all()) and bool((row_of[:-5][live >= experts] == -1).all())
+    placed = row_of[:-5][live < experts]
+    assert sorted(placed.tolist()) == list(range(int(counts.sum())))                                   # every place once
+    firsts = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)[:-1]])
+    for e in range(experts):
+        rows = row_of[:-5][live == e]
+        assert bool(((rows >= firsts[e]) & (rows < firsts[e] + counts[e])).all())
