@@ -127,6 +127,8 @@ def build_from_config(config: dict, compute):
     for name, tensor_spec in expected_tensors(spec).items():
         if tensor_spec.kind == "norm":
             tensor = 1.0 + (torch.rand(tensor_spec.shape, generator=generator, device="cuda") * 0.2 - 0.1)
+        elif tensor_spec.kind == "positive":
+            tensor = 0.1 + 0.9 * torch.rand(tensor_spec.shape, generator=generator, device="cuda")
         elif tensor_spec.kind == "mixing":
             tensor = torch.eye(*tensor_spec.shape, device="cuda") + (torch.rand(tensor_spec.shape, generator=generator, device="cuda") * 0.2 - 0.1)
         else:
@@ -552,6 +554,29 @@ def givelix_config(width: int, heads: int, ff: int, q_rank: int, vocab: int = 32
             "residual_mult": 0.3, "streams": 4, "logit_scale": 0.5, "max_position_embeddings": context}
 
 
+# Fororax at layer sizes that resemble real models of the kind: heads of 128 in groups of eight, six layers in the order
+# [attention_2, attention, attention reading layer 1's keys and values, attention_2, attention_2, attention], every layer
+# with a mixture of eight experts and two identity experts of which a token uses two, beside a shared expert; an expert
+# and the shared one are a third of the Qwen2 feed-forward each, so that a token's work equals the dense layer's.
+FORORAX_SIZES = {
+    "w2048": dict(width=2048, heads=16, ff=8192),
+    "w4096": dict(width=4096, heads=32, ff=16384),
+}
+DESIGN_SIZES = {"givelix": GIVELIX_SIZES, "fororax": FORORAX_SIZES}
+
+
+def fororax_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
+    expert_ff = (ff // 3) // 64 * 64
+    mlp = {"kind": "moe", "router": {"experts": 8, "identity": 2, "top": 2}, "expert": {"ff": expert_ff, "limit": 7.0},
+           "shared": {"ff": ff - 2 * expert_ff, "limit": 7.0}}
+    mixer = {"heads": heads, "kv_heads": max(2, heads // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    kinds = ["attention_2", "attention", "attention", "attention_2", "attention_2", "attention"]
+    layers = [{"type": kind, "mixer": dict(mixer, kv_from=1) if index == 2 else dict(mixer), "mlp": mlp}
+              for index, kind in enumerate(kinds)]
+    return {"architecture": "Fororax", "vocab": vocab, "width": width, "max_positions": context, "layers": layers,
+            "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "embedding": {"scale": 1.0}, "logit_softcap": 30.0}
+
+
 def kernel_times(run, repeats: int = 3) -> dict:
     """Device microseconds per kernel name (a mean over ``repeats`` calls of ``run``), from the profiler's records."""
     import torch
@@ -584,7 +609,7 @@ def kernel_times(run, repeats: int = 3) -> dict:
 
 
 def run_design(args) -> dict:
-    """``--design givelix``: prefill and decode throughput of the Givelix design at two layer sizes beside a Qwen2
+    """``--design NAME``: prefill and decode throughput of the named design at two layer sizes beside a Qwen2
     model of equal width, depth, heads and feed-forward, and the device time of every kernel of a prompt step and a
     decode step, with roofline fractions of the kernels that the two designs do not share."""
     import torch
@@ -599,15 +624,18 @@ def run_design(args) -> dict:
 
     peak = peaks()
     fma_tflops = 2 * 128 * torch.cuda.get_device_properties(0).multi_processor_count * 1.965e9 / 1e12   # float32 FMA pipe
-    batch, out = args.batch, {"design": "givelix", "peaks": dict(peak, fp32_fma_tflops=round(fma_tflops, 1)), "sizes": {}}
-    names = [args.design_size] if args.design_size else list(GIVELIX_SIZES)
+    design = args.design
+    make_config = {"givelix": givelix_config, "fororax": fororax_config}[design]
+    rooflines = {"givelix": design_rooflines, "fororax": fororax_rooflines}[design]
+    batch, out = args.batch, {"design": design, "peaks": dict(peak, fp32_fma_tflops=round(fma_tflops, 1)), "sizes": {}}
+    names = [args.design_size] if args.design_size else list(DESIGN_SIZES[design])
     with ClockSampler() as clocks:
         for size in names:
-            shape = GIVELIX_SIZES[size]
+            shape = DESIGN_SIZES[design][size]
             qwen = dict(QWEN25_1P5B, vocab_size=32768, hidden_size=shape["width"], intermediate_size=shape["ff"],
                         num_hidden_layers=6, num_attention_heads=shape["heads"], num_key_value_heads=max(2, shape["heads"] // 8))
             entry = {}
-            for label, config in (("givelix", givelix_config(**shape)), ("qwen2_equal_size", qwen)):
+            for label, config in ((design, make_config(**shape)), ("qwen2_equal_size", qwen)):
                 model = build_from_config(config, parse_dtype("bfloat16"))
                 prefill_ms = time_prefill(model)
                 decode_ms, _, _, _ = time_decode(model, batch, args.steps, max(args.warmup, 3), repeats=3)
@@ -641,7 +669,7 @@ def run_design(args) -> dict:
                 gc.collect()
                 torch.cuda.empty_cache()
             if not args.quick:
-                entry["roofline"] = design_rooflines(shape, entry, batch, peak, fma_tflops)
+                entry["roofline"] = rooflines(shape, entry, batch, peak, fma_tflops)
             out["sizes"][size] = entry
     out["clocks"] = clocks.summary()
     out["how"] = ("random weights, bfloat16, one 2,048-token prompt per prefill, decode at batch %d over 2,048-token "
@@ -697,6 +725,65 @@ def design_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflop
         q["decode_kernels"], "attn_", 6, batch * tokens * 2 * kv_heads * 128 * 2, 4 * batch * tokens * heads * 128, tensor)
     out["decode"]["qwen2 add_rmsnorm"] = frac(
         q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    return out
+
+
+def fororax_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflops: float) -> dict:
+    """As :func:`design_rooflines`, for Fororax beside Qwen2: the attention kernels (bfloat16 tensor work; attention_2
+    applies every head's weights to the values of every key/value head, which is counted as the work it is), the
+    mixture's products against the dense feed-forward's (the work of the experts that a token uses; bytes of the experts
+    that a step touches), and the row-wise kernels (bytes)."""
+    heads, width, tokens = shape["heads"], shape["width"], PROMPT
+    kv_heads = max(2, heads // 8)
+    config = fororax_config(**shape)
+    mlp = config["layers"][0]["mlp"]
+    expert_ff, shared_ff, experts, top = mlp["expert"]["ff"], mlp["shared"]["ff"], mlp["router"]["experts"], mlp["router"]["top"]
+    bandwidth, tensor, fma = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12, fma_tflops * 1e12
+
+    def frac(kernels: dict, keys, launches_of_work: float, bytes_each: float, flops_each: float, pipe: float):
+        keys = (keys,) if isinstance(keys, str) else keys
+        found = [(name, value) for name, value in kernels.items() if any(key in name for key in keys)]
+        if not found:
+            return None
+        us = sum(value["us"] for _, value in found)
+        count = sum(value["launches"] for _, value in found)
+        bound = max(bytes_each / bandwidth, flops_each / pipe) * launches_of_work
+        return {"us": round(us, 1), "launches": count, "bound_us": round(bound * 1e6, 2), "frac": round(bound * 1e6 / us, 4)}
+
+    pairs = tokens * (tokens + 1) / 2
+    f, q = entry["fororax"], entry["qwen2_equal_size"]
+    out = {"prefill": {}, "decode": {}}
+    # attention: 3 layers of each kind; attention_2 takes Q K^T and P V once per key/value head's values
+    qkv_bytes = tokens * (heads + 2 * kv_heads) * 128 * 2 * 2
+    work = 4 * pairs * heads * 128
+    out["prefill"]["fororax attention (mma.sync; 3 layers with the penalty, 3 with sink and all groups' values)"] = frac(
+        f["prefill_kernels"], "attention_scored_mma", 3 + 3 * kv_heads, qkv_bytes, work, tensor)
+    out["prefill"]["qwen2 attention (tcgen05)"] = frac(q["prefill_kernels"], "attn_", 6, qkv_bytes, work, tensor)
+    # feed-forward products: Qwen2's are library products of [tokens, width] x [3 ff, width]; the mixture's are the
+    # grouped products over the chosen experts' rows and the shared expert's plain products
+    dense_flops = 2 * tokens * width * 3 * shape["ff"]
+    moe_flops = 2 * tokens * width * 3 * (top * (experts / (experts + 2.0)) * expert_ff + shared_ff)   # a fifth of the choices are identity experts
+    out["prefill"]["fororax mixture products (grouped + shared, library)"] = {
+        "work_gflop_a_layer": round(moe_flops / 1e9, 1), "note": "library kernels: see the kernel table for their time"}
+    out["prefill"]["qwen2 feed-forward products (library)"] = {"work_gflop_a_layer": round(dense_flops / 1e9, 1)}
+    out["prefill"]["fororax rows of the mixture (route, place, gather, activation, combine)"] = frac(
+        f["prefill_kernels"], ("moe_",), 6, tokens * width * 2 * (1 + 2 * top) + tokens * top * expert_ff * 2 * 3 + tokens * width * 4 * 2, 0, fma)
+    out["prefill"]["fororax scaled_add_rmsnorm"] = frac(
+        f["prefill_kernels"], "scaled_add_rmsnorm", 12, tokens * width * (4 * 2 + 4 + 2), 0, fma)
+    out["prefill"]["fororax head_norm_kv_write"] = frac(
+        f["prefill_kernels"], "head_norm_kv_write", 6, tokens * (heads + 2 * kv_heads) * 128 * 2 * 2, 0, fma)
+    out["prefill"]["qwen2 add_rmsnorm"] = frac(q["prefill_kernels"], "add_rmsnorm", 13, tokens * width * (4 * 2 + 2 + 2), 0, fma)
+    out["prefill"]["qwen2 rope_kv_write"] = frac(q["prefill_kernels"], "rope_kv_write", 6, tokens * (heads + 2 * kv_heads) * 128 * 2 * 2, 0, fma)
+    # decode step at `batch` requests over 2,048-token contexts
+    kv_bytes = batch * tokens * 2 * kv_heads * 128 * 2
+    out["decode"]["fororax attention (mma.sync, chunks + merge)"] = frac(
+        f["decode_kernels"], ("attention_scored",), 3 + 3 * kv_heads, kv_bytes, 4 * batch * tokens * heads * 128, tensor)
+    out["decode"]["qwen2 attention (mma.sync, split keys)"] = frac(
+        q["decode_kernels"], "attn_", 6, kv_bytes, 4 * batch * tokens * heads * 128, tensor)
+    out["decode"]["fororax scaled_add_rmsnorm"] = frac(f["decode_kernels"], "scaled_add_rmsnorm", 12, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    out["decode"]["fororax rows of the mixture (route, activation)"] = frac(
+        f["decode_kernels"], ("moe_",), 6, (experts + 3) * width * 2 + batch * (experts * expert_ff + shared_ff) * 2 * 3, 0, fma)
+    out["decode"]["qwen2 add_rmsnorm"] = frac(q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
     return out
 
 
@@ -1020,10 +1107,11 @@ def main() -> int:
                         help="with --only: the true float32 path instead of the serving precision")
     parser.add_argument("--quick", action="store_true", help="the headline, its points and the end-to-end number only "
                                                              "(no other model sizes, no float32 point, no kernel table)")
-    parser.add_argument("--design", choices=("givelix",), default=None,
+    parser.add_argument("--design", choices=("givelix", "fororax"), default=None,
                         help="instead of the default workload: the named design at layer sizes of real models beside the "
                              "Qwen2 model of equal size (prefill and decode throughput, kernel times, rooflines)")
-    parser.add_argument("--design-size", choices=tuple(GIVELIX_SIZES), default=None, help="with --design: one size only")
+    parser.add_argument("--design-size", choices=tuple(sorted({name for sizes in DESIGN_SIZES.values() for name in sizes})),
+                        default=None, help="with --design: one size only")
     parser.add_argument("--timeline-json", action="store_true", help="with --timeline: also one JSON line of sums per kind of kernel")
     parser.add_argument("--timeline", type=int, default=0, metavar="LAYERS",
                         help="print the device-side timeline of one decode step (the first LAYERS layers kernel by "

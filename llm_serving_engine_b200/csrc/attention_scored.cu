@@ -270,22 +270,46 @@ __global__ void head_mix_gate_kernel(const float* __restrict__ wide, const float
                                      const TI* __restrict__ gate_proj, int n_partials, long long partial_stride,
                                      long long ld, const float* __restrict__ gate_bias,
                                      const int* __restrict__ segment_of_token, TO* __restrict__ out, int n_q, int n_kv,
-                                     int n_values, int dv) {
+                                     int n_values, int dv, int staged) {
+  extern __shared__ __align__(16) float mix_smem[];   // staged: the token's rows of `wide`, then the mixing table
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   if (segment_of_token[t] < 0) return;
   const int width = n_q * dv;
+  const int row_floats = n_q * n_values * dv;
+  const float* rows = wide + (size_t)t * row_floats;
+  const float* table = mix;
+  if (staged) {   // every output reads n_q of the rows: fetched once, four floats a load, all loads of a thread in flight
+    const float4* src = reinterpret_cast<const float4*>(rows);
+    float4* dst = reinterpret_cast<float4*>(mix_smem);
+    const int pieces = row_floats / 4;
+    for (int base = threadIdx.x; base < pieces; base += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (base + k * blockDim.x < pieces) v[k] = src[base + k * blockDim.x];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (base + k * blockDim.x < pieces) dst[base + k * blockDim.x] = v[k];
+    }
+    if (mix) {
+      float* held = mix_smem + row_floats;
+      for (int e = threadIdx.x; e < n_q * n_q; e += blockDim.x) held[e] = mix[e];
+      table = held;
+    }
+    __syncthreads();
+    rows = mix_smem;
+  }
   for (int e = threadIdx.x; e < width; e += blockDim.x) {
     const int h = e / dv, d = e % dv;
     const int slot = n_values > 1 ? h / (n_q / n_kv) : 0;
     float sum;
     if (mix) {
       sum = 0.f;
-      for (int g = 0; g < n_q; ++g)
-        sum = fmaf(mix[h * n_q + g], wide[(((size_t)t * n_q + g) * n_values + slot) * dv + d], sum);
+      for (int g = 0; g < n_q; ++g) sum = fmaf(table[h * n_q + g], rows[((size_t)g * n_values + slot) * dv + d], sum);
     } else {
-      sum = wide[(((size_t)t * n_q + h) * n_values + slot) * dv + d];
+      sum = rows[((size_t)h * n_values + slot) * dv + d];
     }
     if (gate_proj) {
       float z = 0.f;
@@ -398,9 +422,12 @@ extern "C" int lse_head_mix_gate(const float* wide, const float* mix, const void
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || dv <= 0 || (gate_proj && n_partials < 1)) return LSE_ERR_BAD_ARGUMENT;
   const int n_values = cross ? n_kv : 1;
   const int threads = n_q * dv >= 1024 ? 256 : 128;
+  const size_t row_bytes = sizeof(float) * ((size_t)n_q * n_values * dv + (size_t)n_q * n_q);
+  const int staged = mix != nullptr && row_bytes <= 48 * 1024 && (n_q * n_values * dv) % 4 == 0 && (((uintptr_t)wide) & 15) == 0;
 #define LSE_MIX_CASE(TI, TO)                                                                                        \
-  lse_launch(head_mix_gate_kernel<TI, TO>, tokens, threads, 0, stream, wide, mix, (const TI*)gate_proj, n_partials, \
-             partial_stride, ld, gate_bias, segment_of_token, (TO*)out, n_q, n_kv, n_values, dv)
+  lse_launch(head_mix_gate_kernel<TI, TO>, tokens, threads, staged ? row_bytes : 0, stream, wide, mix,              \
+             (const TI*)gate_proj, n_partials, partial_stride, ld, gate_bias, segment_of_token, (TO*)out, n_q, n_kv,  \
+             n_values, dv, staged)
   if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_MIX_CASE(float, float);
   else if (gate_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_MIX_CASE(__nv_bfloat16, __nv_bfloat16);
   else if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_MIX_CASE(float, __nv_bfloat16);

@@ -6,7 +6,9 @@
 // heads; keys are walked in tiles of 64 through a two-stage cp.async pipeline; causal inside the portion, all of the
 // earlier context before it.  Scores (mma.sync m16n8k16, float32 accumulators), the penalty, the softmax statistics
 // and the output sums are float32; the probabilities are rounded to bfloat16 for the second product.  Everything is
-// kept in base two: s2 = q . k * scale * log2(e) - r1 * log2(1 + r2 * (i - j)).
+// kept in base two: s2 = q . k * scale * log2(e) - r1 * log2(1 + r2 * (i - j)).  The penalty depends on the head and
+// the distance only, and a tile of 64 keys and a few rows has few distances: the block works them out once a tile into
+// a small table (a logarithm per table entry instead of one per score).
 //
 // With `partials` the keys of a tile of rows are cut into chunks of 256 (counted from key 0) with a block each, which
 // leaves (sums, max, total) per row, head, value slot and chunk in the layout of attention_scored.cu; that file's
@@ -42,6 +44,9 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* q_s = smem;                               // [64][DK]
   unsigned char* kv_s = smem + tile_bytes<DK>(BM);         // [2 stages][K [64][DK] | V [64][DV]]
+  // the penalty of this tile's distances, a row per head of the group: entry x of head g is the penalty at distance
+  // x + (position of the tile's first row - the tile's last key); a tile of 64 keys and a few rows has few distances
+  float* pen_s = reinterpret_cast<float*>(kv_s + 2 * (K_BYTES + V_BYTES));
   __shared__ int bt_s[TABLE_STAGE];
   __shared__ int tile_slot[3];
   pdl_launch_dependents();
@@ -83,8 +88,34 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   }
 
   const uint32_t kv_u32 = smem_u32(kv_s);
+  // A 16-key piece of a tile never straddles pages when the page size is a multiple of 16: warp w then copies piece w
+  // of the 64 keys with one look at the block table; else every 16-byte chunk finds its own page.
+  const bool page_pieces = (page_size % 16) == 0 && staged;
   auto load_tile = [&](int kt, int stage) {
     const uint32_t k_dst = kv_u32 + (uint32_t)stage * (K_BYTES + V_BYTES), v_dst = k_dst + K_BYTES;
+    if (page_pieces) {
+      const int j0 = kt * BN + warp * 16;
+      const int limit = j0 <= last_pos ? last_pos + 1 - j0 : 0;   // keys of the piece that exist
+      size_t k_base = 0, v_base = 0;
+      if (limit > 0) {
+        const size_t page = (size_t)bt_s[pm.page(j0)];
+        k_base = ((page * n_kv + kvh) * page_size + pm.offset(j0)) * DK;
+        v_base = ((page * n_kv + value_head) * page_size + pm.offset(j0)) * DV;
+      }
+#pragma unroll
+      for (int i = 0; i < CHK / 2; ++i) {
+        const int n = lane + 32 * i, row = n / CHK, c = n % CHK;
+        const bool valid = row < limit;
+        cp_async16(k_dst + padded_off<DK>(warp * 16 + row, c), kc + k_base + (valid ? row * DK + c * 8 : 0), valid);
+      }
+#pragma unroll
+      for (int i = 0; i < CHV / 2; ++i) {
+        const int n = lane + 32 * i, row = n / CHV, c = n % CHV;
+        const bool valid = row < limit;
+        cp_async16(v_dst + padded_off<DV>(warp * 16 + row, c), vc + v_base + (valid ? row * DV + c * 8 : 0), valid);
+      }
+      return;
+    }
     for (int idx = tid; idx < BN * (CHK + CHV); idx += 128) {
       const bool is_key = idx < BN * CHK;
       const int local = is_key ? idx : idx - BN * CHK;
@@ -117,8 +148,9 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   const int pos_a = pos0 + min(rla, nrows - 1), pos_b = pos0 + min(rlb, nrows - 1);
   const int head_a = kvh * group + ga, head_b = kvh * group + gb;
   const bool penalised = r1 != nullptr;
-  const float r1a = penalised ? r1[head_a] : 0.f, r2a = penalised ? r2[head_a] : 0.f;
-  const float r1b = penalised ? r1[head_b] : 0.f, r2b = penalised ? r2[head_b] : 0.f;
+  const int pen_width = BN + rows_per_tile;
+  const float* pen_a = pen_s + ga * pen_width + rla + (BN - 1);   // minus the key's place in the tile
+  const float* pen_b = pen_s + gb * pen_width + rlb + (BN - 1);
 
   float acc[DV / 8][4];
 #pragma unroll
@@ -129,6 +161,14 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const int stage = (kt - tile_lo) & 1;
     if (kt + 1 < tile_hi) load_tile(kt + 1, stage ^ 1);
     cp_async_commit();
+    if (penalised) {
+      const int nearest = pos0 - (kt * BN + BN - 1);   // distance from the tile's first row to its last key
+      for (int idx = tid; idx < group * pen_width; idx += 128) {
+        const int g = idx / pen_width, distance = idx % pen_width + nearest;
+        const int head = kvh * group + g;
+        pen_s[idx] = distance > 0 ? r1[head] * __log2f(fmaf(r2[head], (float)distance, 1.0f)) : 0.f;
+      }
+    }
     cp_async_wait<1>();
     __syncthreads();
     const uint32_t ks_ = kv_u32 + (uint32_t)stage * (K_BYTES + V_BYTES);
@@ -156,13 +196,11 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     for (int nb = 0; nb < BN / 8; ++nb) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int j = kt * BN + nb * 8 + (lane & 3) * 2 + (e & 1);
+        const int key = nb * 8 + (lane & 3) * 2 + (e & 1);
+        const int j = kt * BN + key;
         const int pos = (e >> 1) ? pos_b : pos_a;
         float v = s[nb][e] * scale_log2e;
-        if (penalised) {
-          const float distance = (float)max(pos - j, 0);
-          v -= ((e >> 1) ? r1b : r1a) * __log2f(fmaf((e >> 1) ? r2b : r2a, distance, 1.0f));
-        }
+        if (penalised) v -= ((e >> 1) ? pen_b : pen_a)[-key];
         if (diagonal && j > pos) v = -INFINITY;
         s[nb][e] = v;
       }
@@ -259,15 +297,17 @@ int launch_scored_mma(const void* q, const void* kc, const void* vc, void* out, 
                       const int* block_tables, int bt_stride, const int* segment_start, const int* segment_first_pos,
                       int num_segments, const float* r1, const float* r2, const float* sink, int tokens, int n_q, int n_kv,
                       int n_values, int page_size, float scale, int num_pages, int max_chunks, cudaStream_t stream) {
-  const size_t smem = (size_t)tile_bytes<D>(BM) + 2 * (size_t)(tile_bytes<D>(BN) + tile_bytes<D>(BN));
+  const int group = n_q / n_kv;
+  const int rows_per_tile = BM / group;
+  const size_t tiles_bytes = (size_t)tile_bytes<D>(BM) + 2 * (size_t)(tile_bytes<D>(BN) + tile_bytes<D>(BN));
+  const size_t smem = tiles_bytes + sizeof(float) * (size_t)group * (BN + rows_per_tile);
   static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_scored_mma_kernel<D, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (!configured) {   // room for the largest penalty table (64 heads a group) once
+    cudaError_t err = cudaFuncSetAttribute(attention_scored_mma_kernel<D, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)(tiles_bytes + sizeof(float) * BM * (BN + 1)));
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  const int group = n_q / n_kv;
-  const int rows_per_tile = BM / group;
   const int tiles = (tokens + rows_per_tile - 1) / rows_per_tile + num_segments;   // every request may end with a partial tile
   const long long depth = (long long)n_values * (partials ? max_chunks : 1);
   if (depth > 65535 || n_kv > 65535) return LSE_ERR_TOO_LARGE;

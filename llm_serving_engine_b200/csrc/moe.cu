@@ -1,11 +1,12 @@
 // Mixture of experts: the router and the experts' gated activation.
 //
-// Router (one block per token, everything float32): z_e = w_e . x over all router outputs (the last `identity` of
-// them are identity experts, whose output is the token's input itself), s = softmax(z), the `top` outputs with the
+// Router (a warp per token, everything float32): the logits z_e = w_e . x over all router outputs come from a matrix
+// product with float32 sums (the last `identity` outputs are identity experts, whose output is the token's input
+// itself; one more column is the shared expert's gate); s = softmax(z), the `top` outputs with the
 // largest s_e + correction_e are chosen (ties: the lower index), and a chosen output's weight is s_e itself, neither
 // corrected nor renormalised.  The kernel leaves a dense row of weights over the real experts (zero where an expert
-// was not chosen), the sum of the chosen identity experts' weights, and the gate of the shared expert,
-// sigmoid(w_sg . x).
+// was not chosen), the choices themselves, the sum of the chosen identity experts' weights, and the gate of the
+// shared expert, sigmoid(w_sg . x).
 //
 // Activation (experts side by side in one product): the row of `gate_up` holds, expert by expert, [gate (ff values) |
 // up (ff values)], then [gate | up] of the shared expert (shared_ff values each); the output row holds the experts'
@@ -22,36 +23,33 @@
 #include "common.cuh"
 
 namespace {
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 128;   // a warp per token
 
-template <typename T>
+// logits: float32 [tokens, ld] (or a stack of n_partials partial sums): the router's outputs, then (has_shared_gate) the
+// shared expert's gate; columns beyond are padding.
 __global__ void __launch_bounds__(ROUTE_THREADS)
-moe_route_kernel(const T* __restrict__ x, const T* __restrict__ router, const float* __restrict__ correction,
-                 const T* __restrict__ shared_gate_w, float* __restrict__ expert_weights,
+moe_route_kernel(const float* __restrict__ logits, int n_partials, long long partial_stride, int ld,
+                 const float* __restrict__ correction, int has_shared_gate, float* __restrict__ expert_weights,
                  float* __restrict__ identity_weight, float* __restrict__ shared_gate, int* __restrict__ chosen_out,
-                 int width, int outputs, int identity, int top) {
-  extern __shared__ float smem[];   // [outputs] scores, [outputs] choice scores
+                 int tokens, int outputs, int identity, int top) {
+  extern __shared__ float smem[];   // per warp: [outputs] scores, [outputs] choice scores
   pdl_launch_dependents();
   pdl_wait();
-  float* score = smem;
-  float* choice = smem + outputs;
-  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const T* row = x + (size_t)t * width;
-  for (int e = warp; e < outputs + (shared_gate_w ? 1 : 0); e += ROUTE_THREADS / 32) {
-    const T* w = e < outputs ? router + (size_t)e * width : shared_gate_w;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (ROUTE_THREADS / 32) + warp;
+  if (t >= tokens) return;
+  float* score = smem + (size_t)warp * 2 * outputs;
+  float* choice = score + outputs;
+  const float* row = logits + (size_t)t * ld;
+  auto logit = [&](int e) {
     float sum = 0.f;
-    for (int i = lane; i < width; i += 32) sum = fmaf(to_f32<T>(row[i]), to_f32<T>(w[i]), sum);
-    sum = warp_sum(sum);
-    if (lane == 0) {
-      if (e < outputs) score[e] = sum;
-      else shared_gate[t] = 1.0f / (1.0f + expf(-sum));
-    }
-  }
-  __syncthreads();
-  if (warp != 0) return;
+    for (int p = 0; p < n_partials; ++p) sum += row[(size_t)p * partial_stride + e];
+    return sum;
+  };
   const int experts = outputs - identity;
   float top_z = -INFINITY;
-  for (int e = lane; e < outputs; e += 32) top_z = fmaxf(top_z, score[e]);
+  for (int e = lane; e < outputs; e += 32) { const float z = logit(e); score[e] = z; top_z = fmaxf(top_z, z); }
+  if (has_shared_gate && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-logit(outputs)));
   top_z = warp_max(top_z);
   float sum = 0.f;
   for (int e = lane; e < outputs; e += 32) sum += expf(score[e] - top_z);
@@ -77,7 +75,11 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ router, const fl
       const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
     }
-    if (best_e >= outputs) break;   // fewer outputs than `top`
+    if (best_e >= outputs) {   // fewer outputs than `top`: the remaining choices are none
+      if (chosen_out && lane == 0)
+        for (int rest = k; rest < top; ++rest) chosen_out[(size_t)t * top + rest] = -1;
+      break;
+    }
     if (lane == 0) {
       choice[best_e] = -INFINITY;
       if (best_e < experts) expert_weights[(size_t)t * experts + best_e] = score[best_e];
@@ -87,6 +89,75 @@ moe_route_kernel(const T* __restrict__ x, const T* __restrict__ router, const fl
     __syncwarp();
   }
   if (lane == 0) identity_weight[t] = identity_sum;
+}
+
+template <typename T> __device__ __forceinline__ void moe_load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void moe_load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void moe_load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void moe_store8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void moe_store8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void moe_store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// Eight columns a thread (ff and shared_ff multiples of 8, rows 16-byte aligned): the same arithmetic as the kernel below.
+template <typename TI, typename TO>
+__global__ void moe_gated_act8_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
+                                      const float* __restrict__ expert_weights, const float* __restrict__ shared_gate,
+                                      TO* __restrict__ out, int experts, int ff, int shared_ff, float limit,
+                                      float shared_limit) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int inter = experts * ff + shared_ff;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (i >= inter) return;
+  const bool shared = i >= experts * ff;
+  const float c = shared ? (shared_gate ? shared_gate[t] : 1.f)
+                         : (expert_weights ? expert_weights[(size_t)t * experts + i / ff] : 1.f);
+  TO* dst = out + (size_t)t * inter + i;
+  float y[8];
+  if (c == 0.f) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = 0.f;
+    moe_store8<TO>(dst, y);
+    return;
+  }
+  const TI* row = gate_up + (size_t)t * 2 * inter;
+  const int gate_at = shared ? 2 * experts * ff + (i - experts * ff) : (i / ff) * 2 * ff + i % ff;
+  const int up_at = gate_at + (shared ? shared_ff : ff);
+  float g[8], u[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) g[e] = u[e] = 0.f;
+  for (int p = 0; p < n_partials; ++p) {
+    float a[8], b[8];
+    moe_load8<TI>(row + (size_t)p * partial_stride + gate_at, a);
+    moe_load8<TI>(row + (size_t)p * partial_stride + up_at, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { g[e] += a[e]; u[e] += b[e]; }
+  }
+  const float lim = shared ? shared_limit : limit;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float gc = fminf(g[e], lim), uc = fminf(fmaxf(u[e], -lim), lim);
+    y[e] = c * (gc / (1.0f + expf(-1.702f * gc)) * (uc + 1.0f));
+  }
+  moe_store8<TO>(dst, y);
 }
 
 template <typename TI, typename TO>
@@ -175,6 +246,34 @@ __global__ void moe_combine_kernel(const T* __restrict__ down, const int* __rest
   pdl_wait();
   const int t = blockIdx.x;
   const float identity = identity_weight ? identity_weight[t] : 0.f;
+  if (width % 8 == 0) {   // eight columns a thread (rows are 16-byte aligned then)
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      float sum[8];
+      if (accumulate) moe_load8<float>(y + (size_t)t * width + i, sum);
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum[e] = 0.f;
+      }
+      for (int k = 0; k < top; ++k) {
+        const int row = row_of[t * top + k];
+        if (row >= 0) {
+          const float w = expert_weights[(size_t)t * experts + chosen[t * top + k]];
+          float v[8];
+          moe_load8<T>(down + (size_t)row * width + i, v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) sum[e] = fmaf(w, v[e], sum[e]);
+        }
+      }
+      if (identity != 0.f) {
+        float v[8];
+        moe_load8<T>(x + (size_t)t * width + i, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum[e] = fmaf(identity, v[e], sum[e]);
+      }
+      moe_store8<float>(y + (size_t)t * width + i, sum);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float sum = accumulate ? y[(size_t)t * width + i] : 0.f;
     for (int k = 0; k < top; ++k) {
@@ -188,26 +287,23 @@ __global__ void moe_combine_kernel(const T* __restrict__ down, const int* __rest
 }
 }  // namespace
 
-// x, router [outputs, width], shared_gate_w [width] (or null) in one dtype; correction float32 [outputs] or null.
+// logits float32 [tokens, ld] or n_partials partial sums partial_stride apart: column e < outputs is router output e,
+// column `outputs` the shared expert's gate (has_shared_gate); correction float32 [outputs] or null.
 // expert_weights float32 [tokens, outputs - identity]; identity_weight, shared_gate float32 [tokens];
-// chosen int32 [tokens, top] or null.
-extern "C" int lse_moe_route(const void* x, const void* router, const float* correction, const void* shared_gate_w,
-                             int dtype, float* expert_weights, float* identity_weight, float* shared_gate, int* chosen,
-                             int tokens, int width, int outputs, int identity, int top, cudaStream_t stream) {
+// chosen int32 [tokens, top] or null (-1 where there are fewer outputs than top).
+extern "C" int lse_moe_route(const float* logits, int n_partials, long long partial_stride, int ld, const float* correction,
+                             int has_shared_gate, float* expert_weights, float* identity_weight, float* shared_gate,
+                             int* chosen, int tokens, int outputs, int identity, int top, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (outputs <= 0 || identity < 0 || identity > outputs || top <= 0 || width <= 0) return LSE_ERR_BAD_ARGUMENT;
-  if (outputs > 4096) return LSE_ERR_TOO_LARGE;
-  const size_t smem = sizeof(float) * 2 * (size_t)outputs;
-  if (dtype == LSE_DTYPE_F32)
-    lse_launch(moe_route_kernel<float>, tokens, ROUTE_THREADS, smem, stream, (const float*)x, (const float*)router,
-               correction, (const float*)shared_gate_w, expert_weights, identity_weight, shared_gate, chosen, width,
-               outputs, identity, top);
-  else if (dtype == LSE_DTYPE_BF16)
-    lse_launch(moe_route_kernel<__nv_bfloat16>, tokens, ROUTE_THREADS, smem, stream, (const __nv_bfloat16*)x,
-               (const __nv_bfloat16*)router, correction, (const __nv_bfloat16*)shared_gate_w, expert_weights,
-               identity_weight, shared_gate, chosen, width, outputs, identity, top);
-  else
+  if (outputs <= 0 || identity < 0 || identity > outputs || top <= 0 || n_partials < 1 ||
+      ld < outputs + (has_shared_gate ? 1 : 0))
     return LSE_ERR_BAD_ARGUMENT;
+  if (outputs > 1024) return LSE_ERR_TOO_LARGE;
+  const int warps = ROUTE_THREADS / 32;
+  const size_t smem = sizeof(float) * 2 * (size_t)outputs * warps;
+  lse_launch(moe_route_kernel, (tokens + warps - 1) / warps, ROUTE_THREADS, smem, stream, logits, n_partials,
+             partial_stride, ld, correction, has_shared_gate, expert_weights, identity_weight, shared_gate, chosen, tokens,
+             outputs, identity, top);
   LSE_LAUNCH_CHECK();
 }
 
@@ -219,13 +315,19 @@ extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partia
   const int inter = experts * ff + shared_ff;
   if (inter <= 0 || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   if ((inter + 255) / 256 > 65535) return LSE_ERR_TOO_LARGE;
-  const dim3 grid(tokens, (inter + 255) / 256);
-#define LSE_MOE_ACT_CASE(TI, TO)                                                                                   \
-  lse_launch(moe_gated_act_kernel<TI, TO>, grid, 256, 0, stream, (const TI*)gate_up, n_partials, partial_stride,   \
-             expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit)
-  if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_MOE_ACT_CASE(float, float);
-  else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_MOE_ACT_CASE(__nv_bfloat16, __nv_bfloat16);
-  else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_MOE_ACT_CASE(float, __nv_bfloat16);
+  const bool wide = ff % 8 == 0 && shared_ff % 8 == 0 && partial_stride % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
+  const dim3 grid(tokens, wide ? (inter / 8 + 127) / 128 : (inter + 255) / 256);
+  const int threads = wide ? 128 : 256;
+#define LSE_MOE_ACT_CASE(TI, TO)                                                                                      \
+  if (wide)                                                                                                           \
+    lse_launch(moe_gated_act8_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)gate_up, n_partials, partial_stride, \
+               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit);                   \
+  else                                                                                                                \
+    lse_launch(moe_gated_act_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)gate_up, n_partials, partial_stride,  \
+               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit)
+  if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_MOE_ACT_CASE(float, float); }
+  else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_MOE_ACT_CASE(__nv_bfloat16, __nv_bfloat16); }
+  else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_MOE_ACT_CASE(float, __nv_bfloat16); }
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_MOE_ACT_CASE
   LSE_LAUNCH_CHECK();

@@ -4,7 +4,7 @@
 //     in the compute dtype as the next branch's input;
 //   * RMS norm of every head's query and key (one weight shared by the heads), bias, and the write of keys and values
 //     into the paged cache (keys and values may have different head sizes);
-//   * y[t] += c_t x[t];  logits <- cap tanh(logits / cap).
+//   * logits <- cap tanh(logits / cap).
 // An input that comes from a matrix product may be a stack of float32 partial sums, added in index order first.
 // All arithmetic is float32; a value is rounded once, when it is stored in a bfloat16 tensor.
 #include "common.cuh"
@@ -12,6 +12,28 @@
 LSE_CHECK_DEFINE(lse_check_rowwise_postnorm)
 
 namespace {
+
+template <typename T> __device__ __forceinline__ void postnorm_load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void postnorm_load4<float>(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <> __device__ __forceinline__ void postnorm_load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T> __device__ __forceinline__ void postnorm_store4(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void postnorm_store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void postnorm_store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
 
 // ------------------------------------------------------------------ embedding + learned positions
 template <typename T, typename TO>
@@ -73,6 +95,93 @@ __global__ void scaled_add_rmsnorm_kernel(float* __restrict__ residual, const TD
   }
 }
 
+// The same for rows whose width is a multiple of 4 up to 256 * 4 * C: the row stays in registers between the sum of
+// squares and the write (a thread owns C float4 pieces), the partial sums are fetched four at a time, one barrier
+// pair.  Few rows (decoding) wait for round trips, not for bandwidth: this form has three of them.
+template <typename TD, typename TO, int C>
+__global__ void __launch_bounds__(256)
+scaled_add_rmsnorm_regs_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_partials,
+                               long long partial_stride, const float* __restrict__ bias,
+                               const float* __restrict__ row_scale, float alpha, const float* __restrict__ weight,
+                               TO* __restrict__ hidden_io, int hidden, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  float* res = residual + (size_t)t * hidden;
+  const TD* del = delta ? delta + (size_t)t * hidden : nullptr;
+  TO* hid = hidden_io ? hidden_io + (size_t)t * hidden : nullptr;
+  const float extra = row_scale ? row_scale[t] : 0.f;
+  const int pieces = hidden / 4;
+  float y[C][4];
+  float sq = 0.f;
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const int piece = threadIdx.x + c * 256;
+    if (piece < pieces) {
+      const int i = piece * 4;
+      float x[4], sum[4] = {0.f, 0.f, 0.f, 0.f};
+      postnorm_load4<float>(res + i, x);
+      if (del) {
+        int p = 0;
+        for (; p + 8 <= n_partials; p += 8) {   // eight loads in flight, added in index order
+          float a[8][4];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) postnorm_load4<TD>(del + (size_t)(p + k) * partial_stride + i, a[k]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum[e] += a[k][e];
+        }
+        for (; p + 4 <= n_partials; p += 4) {
+          float a[4][4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) postnorm_load4<TD>(del + (size_t)(p + k) * partial_stride + i, a[k]);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum[e] += a[k][e];
+        }
+        for (; p < n_partials; ++p) {
+          float a[4];
+          postnorm_load4<TD>(del + (size_t)p * partial_stride + i, a);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sum[e] += a[e];
+        }
+      }
+      if (bias) {
+        float b[4];
+        postnorm_load4<float>(bias + i, b);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sum[e] += b[e];
+      }
+      if (row_scale) {
+        float h[4];
+        if (hid) postnorm_load4<TO>(hid + i, h);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sum[e] = fmaf(extra, hid ? h[e] : x[e], sum[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { y[c][e] = fmaf(alpha, x[e], sum[e]); sq = fmaf(y[c][e], y[c][e], sq); }
+    }
+  }
+  const float total = block_sum(sq, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const int piece = threadIdx.x + c * 256;
+    if (piece < pieces) {
+      const int i = piece * 4;
+      float w[4], r[4];
+      postnorm_load4<float>(weight + i, w);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) r[e] = (y[c][e] * inv) * w[e];
+      postnorm_store4<float>(res + i, r);
+      if (hid) postnorm_store4<TO>(hid + i, r);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ per-head norm of queries and keys, cache write
 // A warp owns one head of one token: items 0 .. n_q-1 are query heads, then n_kv key heads, then n_kv value heads.
 // The row of `proj` is [q (n_q * dk) | k (n_kv * dk) | v (n_kv * dv) | anything else].
@@ -115,28 +224,63 @@ __global__ void head_norm_kv_write_kernel(const TI* __restrict__ proj, int n_par
     for (int p = 0; p < n_partials; ++p) sum += to_f32<TI>(src[(size_t)p * partial_stride + i]);
     return bias ? sum + bias[column + i] : sum;
   };
-  float inv = 1.f;
-  if (norm_w) {
+  // Four consecutive values a load when the head's width and place allow (every operand 16- or 8-byte aligned).
+  const bool by_four = width % 4 == 0 && column % 4 == 0 && ld % 4 == 0 && partial_stride % 4 == 0 && width <= 512;
+  if (by_four) {
+    float kept[4][4];   // pieces lane, lane + 32, ... of the head
     float sq = 0.f;
-    for (int i = lane; i < width; i += 32) { const float x = value(i); sq = fmaf(x, x, sq); }
-    inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = (lane + 32 * k) * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) kept[k][e] = 0.f;
+      if (i < width) {
+        for (int p = 0; p < n_partials; ++p) {
+          float a[4];
+          postnorm_load4<TI>(src + (size_t)p * partial_stride + i, a);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) kept[k][e] += a[e];
+        }
+        if (bias) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) kept[k][e] += bias[column + i + e];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sq = fmaf(kept[k][e], kept[k][e], sq);
+      }
+    }
+    const float inv = norm_w ? 1.0f / sqrtf(warp_sum(sq) / (float)width + eps) : 1.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int i = (lane + 32 * k) * 4;
+      if (i < width) {
+        float r[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) r[e] = norm_w ? (kept[k][e] * inv) * norm_w[i + e] : kept[k][e];
+        postnorm_store4<TO>(dst + i, r);
+      }
+    }
+    return;
   }
-  for (int i = lane; i < width; i += 32) {
+  constexpr int KEPT = 8;   // values a lane keeps between the sum of squares and the write (heads up to 256 wide)
+  float kept[KEPT];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < KEPT; ++k) {
+    const int i = lane + 32 * k;
+    kept[k] = i < width ? value(i) : 0.f;
+    sq = fmaf(kept[k], kept[k], sq);
+  }
+  for (int i = lane + 32 * KEPT; i < width; i += 32) { const float x = value(i); sq = fmaf(x, x, sq); }
+  const float inv = norm_w ? 1.0f / sqrtf(warp_sum(sq) / (float)width + eps) : 1.f;
+#pragma unroll
+  for (int k = 0; k < KEPT; ++k) {
+    const int i = lane + 32 * k;
+    if (i < width) dst[i] = from_f32<TO>(norm_w ? (kept[k] * inv) * norm_w[i] : kept[k]);
+  }
+  for (int i = lane + 32 * KEPT; i < width; i += 32) {
     const float x = value(i);
     dst[i] = from_f32<TO>(norm_w ? (x * inv) * norm_w[i] : x);
-  }
-}
-
-template <typename TY, typename TX>
-__global__ void add_scaled_rows_kernel(TY* __restrict__ y, const float* __restrict__ row_scale, const TX* __restrict__ x,
-                                       int hidden) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int t = blockIdx.x;
-  const float c = row_scale[t];
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const size_t at = (size_t)t * hidden + i;
-    y[at] = from_f32<TY>(fmaf(c, to_f32<TX>(x[at]), to_f32<TY>(y[at])));
   }
 }
 
@@ -175,15 +319,22 @@ extern "C" int lse_scaled_add_rmsnorm(float* residual, const void* delta, int de
   if (tokens <= 0) return 0;
   if (delta && n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   const int threads = hidden >= 2048 ? 256 : 128;
+  const int pieces = hidden % 4 == 0 && partial_stride % 4 == 0 ? (hidden / 4 + 255) / 256 : 0;   // float4 pieces a thread
+#define LSE_POSTNORM_ARGS(TD, TO) residual, (const TD*)delta, n_partials, partial_stride, bias, row_scale, alpha, weight, \
+  (TO*)hidden_io, hidden, eps
 #define LSE_POSTNORM_CASE(TD, TO)                                                                                   \
-  lse_launch(scaled_add_rmsnorm_kernel<TD, TO>, tokens, threads, 0, stream, residual, (const TD*)delta, n_partials, \
-             partial_stride, bias, row_scale, alpha, weight, (TO*)hidden_io, hidden, eps)
-  if (delta_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_POSTNORM_CASE(float, float);
-  else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_POSTNORM_CASE(__nv_bfloat16, __nv_bfloat16);
-  else if (delta_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_POSTNORM_CASE(float, __nv_bfloat16);
-  else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_F32) LSE_POSTNORM_CASE(__nv_bfloat16, float);
+  if (pieces == 1) lse_launch(scaled_add_rmsnorm_regs_kernel<TD, TO, 1>, tokens, 256, 0, stream, LSE_POSTNORM_ARGS(TD, TO)); \
+  else if (pieces == 2) lse_launch(scaled_add_rmsnorm_regs_kernel<TD, TO, 2>, tokens, 256, 0, stream, LSE_POSTNORM_ARGS(TD, TO)); \
+  else if (pieces >= 3 && pieces <= 4) lse_launch(scaled_add_rmsnorm_regs_kernel<TD, TO, 4>, tokens, 256, 0, stream, LSE_POSTNORM_ARGS(TD, TO)); \
+  else if (pieces >= 5 && pieces <= 8) lse_launch(scaled_add_rmsnorm_regs_kernel<TD, TO, 8>, tokens, 256, 0, stream, LSE_POSTNORM_ARGS(TD, TO)); \
+  else lse_launch(scaled_add_rmsnorm_kernel<TD, TO>, tokens, threads, 0, stream, LSE_POSTNORM_ARGS(TD, TO))
+  if (delta_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_POSTNORM_CASE(float, float); }
+  else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_POSTNORM_CASE(__nv_bfloat16, __nv_bfloat16); }
+  else if (delta_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_POSTNORM_CASE(float, __nv_bfloat16); }
+  else if (delta_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_F32) { LSE_POSTNORM_CASE(__nv_bfloat16, float); }
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_POSTNORM_CASE
+#undef LSE_POSTNORM_ARGS
   LSE_LAUNCH_CHECK();
 }
 
@@ -209,23 +360,6 @@ extern "C" int lse_head_norm_kv_write(const void* proj, int in_dtype, int n_part
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_HEADNORM_CASE(float, __nv_bfloat16);
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_HEADNORM_CASE
-  LSE_LAUNCH_CHECK();
-}
-
-extern "C" int lse_add_scaled_rows(void* y, int y_dtype, const float* row_scale, const void* x, int x_dtype, int tokens,
-                                   int hidden, cudaStream_t stream) {
-  if (tokens <= 0) return 0;
-  const int threads = hidden >= 1024 ? 256 : 128;
-  if (y_dtype == LSE_DTYPE_F32 && x_dtype == LSE_DTYPE_F32)
-    lse_launch(add_scaled_rows_kernel<float, float>, tokens, threads, 0, stream, (float*)y, row_scale, (const float*)x, hidden);
-  else if (y_dtype == LSE_DTYPE_F32 && x_dtype == LSE_DTYPE_BF16)
-    lse_launch(add_scaled_rows_kernel<float, __nv_bfloat16>, tokens, threads, 0, stream, (float*)y, row_scale,
-               (const __nv_bfloat16*)x, hidden);
-  else if (y_dtype == LSE_DTYPE_BF16 && x_dtype == LSE_DTYPE_BF16)
-    lse_launch(add_scaled_rows_kernel<__nv_bfloat16, __nv_bfloat16>, tokens, threads, 0, stream, (__nv_bfloat16*)y,
-               row_scale, (const __nv_bfloat16*)x, hidden);
-  else
-    return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
 }
 

@@ -82,10 +82,9 @@ _SIGNATURES = {
     "lse_head_norm_kv_write": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_void_p],
-    "lse_add_scaled_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lse_softcap": [c_void_p, c_longlong, c_float, c_void_p],
-    "lse_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                      c_int, c_int, c_int, c_int, c_void_p],
+    "lse_moe_route": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_int, c_int, c_void_p],
     "lse_moe_gated_act": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_int, c_float, c_float, c_void_p],
     "lse_moe_group_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],

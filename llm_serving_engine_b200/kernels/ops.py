@@ -779,15 +779,6 @@ def softcap(values: torch.Tensor, cap: float) -> torch.Tensor:
     return values
 
 
-def add_scaled_rows(y: torch.Tensor, row_scale: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
-    """y[t] += row_scale[t] * x[t]; y, x [T, H]; row_scale float32 [T]."""
-    _need_cuda(y, row_scale, x)
-    assert y.shape == x.shape and y.is_contiguous() and x.is_contiguous() and row_scale.dtype == torch.float32
-    check(library.load().lse_add_scaled_rows(y.data_ptr(), dtype_code(y.dtype), row_scale.data_ptr(), x.data_ptr(),
-                                             dtype_code(x.dtype), y.shape[0], y.shape[1], _stream()), "add_scaled_rows")
-    return y
-
-
 # ------------------------------------------------------------------ attention with normed heads and changed scores
 def head_norm_kv_write(proj: torch.Tensor, bias: torch.Tensor | None, q_norm: torch.Tensor | None,
                        k_norm: torch.Tensor | None, eps: float, slot_mapping: torch.Tensor | None, q_out: torch.Tensor,
@@ -909,27 +900,28 @@ def head_mix_gate(wide: torch.Tensor, mix: torch.Tensor | None, gate_proj: torch
 
 
 # ------------------------------------------------------------------ mixture of experts
-def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, shared_gate_w: torch.Tensor | None,
-              identity: int, top: int, chosen: torch.Tensor | None = None):
-    """The router of a mixture of experts, in float32: scores softmax(x router^T) over all outputs (the last
-    ``identity`` of them identity experts), the ``top`` largest of score + ``correction`` chosen, weights the scores
-    themselves.  Returns (expert_weights float32 [T, experts], zero where not chosen; identity_weight float32 [T],
-    the chosen identity experts' weights added up; shared_gate float32 [T] = sigmoid(x . shared_gate_w), or None)."""
-    _need_cuda(x, router, correction, shared_gate_w, chosen)
-    tokens, width = x.shape
-    outputs = router.shape[0]
-    assert x.is_contiguous() and router.is_contiguous() and router.shape[1] == width and router.dtype == x.dtype
+def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, outputs: int, identity: int, top: int,
+              shared_gate: bool = False, chosen: torch.Tensor | None = None):
+    """The router of a mixture of experts, in float32.  ``logits`` float32 [T, N] (or a stack of partial sums [P, T, N]):
+    column e < ``outputs`` is router output e (the last ``identity`` of them identity experts), column ``outputs`` the
+    pre-activation of the shared expert's gate when ``shared_gate``; further columns are padding.  Scores softmax(z)
+    over the outputs, the ``top`` largest of score + ``correction`` chosen, weights the scores themselves.  Returns
+    (expert_weights float32 [T, experts], zero where not chosen; identity_weight float32 [T], the chosen identity
+    experts' weights added up; the shared gate float32 [T] = sigmoid of its column, or None).  ``chosen`` int32
+    [T, top] receives the choices."""
+    _need_cuda(logits, correction, chosen)
+    logits, code, n_partials, stride, ld = _projection(logits)
+    tokens = logits.shape[-2]
+    assert code == F32 and logits.shape[-1] >= outputs + int(shared_gate)
     assert correction is None or (correction.dtype == torch.float32 and correction.shape == (outputs,))
-    assert shared_gate_w is None or (shared_gate_w.dtype == x.dtype and shared_gate_w.numel() == width and shared_gate_w.is_contiguous())
     assert chosen is None or (chosen.dtype == torch.int32 and chosen.shape == (tokens, top) and chosen.is_contiguous())
-    expert_weights = torch.empty((tokens, outputs - identity), dtype=torch.float32, device=x.device)
-    identity_weight = torch.empty((tokens,), dtype=torch.float32, device=x.device)
-    shared_gate = torch.empty((tokens,), dtype=torch.float32, device=x.device) if shared_gate_w is not None else None
-    check(library.load().lse_moe_route(x.data_ptr(), router.data_ptr(), _ptr(correction), _ptr(shared_gate_w),
-                                       dtype_code(x.dtype), expert_weights.data_ptr(), identity_weight.data_ptr(),
-                                       _ptr(shared_gate), _ptr(chosen), tokens, width, outputs, int(identity), int(top),
-                                       _stream()), "moe_route")
-    return expert_weights, identity_weight, shared_gate
+    expert_weights = torch.empty((tokens, outputs - identity), dtype=torch.float32, device=logits.device)
+    identity_weight = torch.empty((tokens,), dtype=torch.float32, device=logits.device)
+    gate = torch.empty((tokens,), dtype=torch.float32, device=logits.device) if shared_gate else None
+    check(library.load().lse_moe_route(logits.data_ptr(), n_partials, stride, ld, _ptr(correction), int(shared_gate),
+                                       expert_weights.data_ptr(), identity_weight.data_ptr(), _ptr(gate), _ptr(chosen),
+                                       tokens, int(outputs), int(identity), int(top), _stream()), "moe_route")
+    return expert_weights, identity_weight, gate
 
 
 def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_gate: torch.Tensor | None,

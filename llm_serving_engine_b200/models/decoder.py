@@ -152,9 +152,12 @@ class DecoderModel:
             for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
                 if part is None:
                     continue
+                held: dict[int, int] = {}     # a part may keep views of a matrix beside it: every storage counts once
                 for value in vars(part).values():
                     if isinstance(value, torch.Tensor) and value.dim() >= 1 and value.is_floating_point():
-                        total += value.numel() * value.element_size()
+                        key = value.untyped_storage().data_ptr()
+                        held[key] = max(held.get(key, 0), value.numel() * value.element_size())
+                total += sum(held.values())
         return total
 
     def forward(self, step, caches) -> torch.Tensor:

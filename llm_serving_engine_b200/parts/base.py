@@ -84,7 +84,7 @@ class ResidualStream:
     applies all of it (``Norm.forward``)."""
 
     __slots__ = ("residual", "delta", "copies", "delta_mult", "delta_scale", "mix", "write", "read", "hidden",
-                 "delta_bias")
+                 "delta_bias", "delta_row_scale")
 
     def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None, copies: int = 1) -> None:
         self.residual = residual
@@ -100,6 +100,7 @@ class ResidualStream:
         # float32), and a bias (float32 [H]) that belongs to the pending output.
         self.hidden = None
         self.delta_bias = None
+        self.delta_row_scale = None   # float32 [T] c: c_t times the branch's input row belongs to the pending output too
 
     @property
     def plain(self) -> bool:
@@ -153,6 +154,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    row_scale = None       # set by forward: float32 [T] c, when c_t x_t is part of the output and left to the next norm
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 

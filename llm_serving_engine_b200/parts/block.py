@@ -91,4 +91,5 @@ class PostNormResidualBlock(Block):
         x = self.mixer_norm.forward(stream)
         if self.feed_forward is not None:
             stream.delta = self.feed_forward.forward(x)
+            stream.delta_row_scale = self.feed_forward.row_scale
             self.feed_forward_norm.forward(stream)

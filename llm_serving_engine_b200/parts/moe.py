@@ -59,9 +59,16 @@ class ClampedMoE(FeedForward):
         self.inter = self.experts * self.ff + self.shared_ff
         self.gate_up_weight = torch.cat(pairs, dim=0).contiguous() if prefixes else None
         self.down_weight = torch.cat([weights[prefix + names["down"]] for prefix in prefixes], dim=1).contiguous() if prefixes else None
-        self.router = weights[names["router"]].contiguous()
+        # the router's rows, then the shared expert's gate row, padded with zero rows to a multiple of 16: one product
+        # gives every logit that the routing kernel reads
+        rows = [weights[names["router"]]] + ([weights[names["shared"] + names["shared_gate"]].reshape(1, -1)] if shared else [])
+        self.outputs = self.experts + self.identity
+        pad = -(self.outputs + len(rows) - 1) % 16
+        if pad:
+            rows.append(torch.zeros((pad, rows[0].shape[1]), dtype=rows[0].dtype, device=rows[0].device))
+        self.router = torch.cat(rows, dim=0).contiguous()
         self.correction = weights[names["correction"]].float().contiguous() if p.get("correction", True) else None
-        self.shared_gate_w = weights[names["shared"] + names["shared_gate"]].reshape(-1).contiguous() if shared else None
+        self.row_scale = None    # after forward: float32 [T] c_t, when c_t x_t is still to be added to the output
         # views of the stacked matrices for the grouped product: [experts, width, 2 ff] and [experts, ff, width]
         self._grouped_gate_up = self._grouped_down = None
         width = self.router.shape[1]
@@ -93,14 +100,13 @@ class ClampedMoE(FeedForward):
         """Rows grouped by expert (see the class)."""
         tokens, width = x.shape
         chosen = torch.empty((tokens, self.top), dtype=torch.int32, device=x.device)
-        expert_weights, identity_weight, shared_gate = ops.moe_route(x, self.router, self.correction, self.shared_gate_w,
-                                                                     self.identity, self.top, chosen)
+        expert_weights, identity_weight, shared_gate = self._route(x, chosen)
         y = None
         if self.shared_ff:   # the shared expert: two plain products, its gate folded into the activation
             routed = self.experts * self.ff
             gate_up = linear(x, self.gate_up_weight[2 * routed:])
             act = torch.empty((tokens, self.shared_ff), dtype=x.dtype, device=x.device)
-            ops.moe_gated_act(gate_up, None, shared_gate, act, 0, 1, self.shared_ff, self.limit, self.shared_limit)
+            ops.moe_gated_act(gate_up, None, shared_gate, act, 0, 8, self.shared_ff, self.limit, self.shared_limit)
             y = linear(act, self.down_weight[:, routed:], out_dtype=torch.float32)
         row_of, offsets = ops.moe_group_rows(chosen, self.experts)
         rows = tokens * self.top
@@ -114,23 +120,34 @@ class ClampedMoE(FeedForward):
         return ops.moe_combine(down, row_of, chosen, expert_weights, identity_weight if self.identity else None, x, out,
                                accumulate=y is not None)
 
+    def _route(self, x, chosen=None):
+        """The router's logits as a product with float32 sums (partial sums for few rows), then the routing kernel."""
+        if x.dtype != torch.bfloat16:
+            logits = linear_partials(x, self.router)
+        elif x.shape[0] <= SKINNY_MAX_ROWS and ops.gemm_bf16_skinny_ok(x, self.router):
+            logits = ops.gemm_bf16_skinny(x, self.router)     # float32 partial sums, added up by the routing kernel
+        else:
+            logits = linear(x, self.router, out_dtype=torch.float32)
+        return ops.moe_route(logits, self.correction, self.outputs, self.identity, self.top,
+                             shared_gate=self.shared_ff > 0, chosen=chosen)
+
     def forward(self, x):
         tokens = x.shape[0]
+        self.row_scale = None
         if self._grouped_gate_up is not None and x.dtype == torch.bfloat16 and tokens >= GROUPED_FROM_ROWS:
             return self._grouped(x)
-        expert_weights, identity_weight, shared_gate = ops.moe_route(x, self.router, self.correction, self.shared_gate_w,
-                                                                     self.identity, self.top)
+        expert_weights, identity_weight, shared_gate = self._route(x)
         if self.inter:
             gate_up = linear_partials(x, self.gate_up_weight)
             act = torch.empty((tokens, self.inter), dtype=x.dtype, device=x.device)
             ops.moe_gated_act(gate_up, expert_weights, shared_gate, act, self.experts, self.ff, self.shared_ff,
                               self.limit, self.shared_limit)
             if x.dtype == torch.bfloat16 and tokens > SKINNY_MAX_ROWS:
-                y = linear(act, self.down_weight, out_dtype=torch.float32)   # the identity experts' share is added in float32
+                y = linear(act, self.down_weight, out_dtype=torch.float32)
             else:
                 y = linear_partials(act, self.down_weight)
         else:
             y = torch.zeros((tokens, x.shape[1]), dtype=torch.float32, device=x.device)
         if self.identity:
-            ops.add_scaled_rows(y[0] if y.dim() == 3 else y, identity_weight, x)
+            self.row_scale = identity_weight     # the identity experts' share w_t x_t: the norm that adds the output adds it
         return y

@@ -53,7 +53,8 @@ class RMSNormAfterSum(Norm):
     """params: ``eps``, ``residual_mult`` (alpha), ``weight_name`` (default "weight").
 
     The norm of a layer that normalises after the sum: x <- (alpha x + y + b) / sqrt(mean((alpha x + y + b)^2) + eps) * w,
-    where y is the pending branch output and b the bias that came with it.  The result replaces the float32 residual
+    where y is the pending branch output and b the bias that came with it (and c_t x_t, when the branch left a factor
+    per row on its own input, ``stream.delta_row_scale``).  The result replaces the float32 residual
     and, rounded, ``stream.hidden``, which the next branch reads; the rounded rows are returned."""
 
     graph_safe = True
@@ -72,7 +73,7 @@ class RMSNormAfterSum(Norm):
         if rows is not None or not stream.plain:
             raise ops.KernelError("rmsnorm_after_sum: the norm runs over all rows of one copy of the residual")
         copy = stream.hidden if stream.hidden is not stream.residual else None
-        ops.scaled_add_rmsnorm(stream.residual, stream.delta, stream.delta_bias, None, self.alpha, self.weight,
-                               self.eps, copy)
-        stream.delta = stream.delta_bias = None
+        ops.scaled_add_rmsnorm(stream.residual, stream.delta, stream.delta_bias, stream.delta_row_scale, self.alpha,
+                               self.weight, self.eps, copy)
+        stream.delta = stream.delta_bias = stream.delta_row_scale = None
         return stream.hidden
