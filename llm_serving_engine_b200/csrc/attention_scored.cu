@@ -265,12 +265,34 @@ attention_scored_merge_kernel(const float* __restrict__ partials, TO* __restrict
 // out[t, h, d] = gate * sum_g mix[h, g] * wide[t, g, slot(h), d], with slot(h) = h / (n_q / n_kv) when the wide rows hold
 // a value slot per key/value head (n_values > 1), else wide[t, h, 0, d] (mix null: the identity);
 // gate = sigmoid(sum_p gate_proj[p][t, column] + gate_bias[column]) (gate_proj null: 1).
+template <typename T> __device__ __forceinline__ void scored_load4(const T* p, float (&v)[4]);
+template <> __device__ __forceinline__ void scored_load4<float>(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+template <> __device__ __forceinline__ void scored_load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T> __device__ __forceinline__ void scored_store4(T* p, const float (&v)[4]);
+template <> __device__ __forceinline__ void scored_store4<float>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void scored_store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename TI, typename TO>
 __global__ void head_mix_gate_kernel(const float* __restrict__ wide, const float* __restrict__ mix,
                                      const TI* __restrict__ gate_proj, int n_partials, long long partial_stride,
                                      long long ld, const float* __restrict__ gate_bias,
                                      const int* __restrict__ segment_of_token, TO* __restrict__ out, int n_q, int n_kv,
-                                     int n_values, int dv, int staged) {
+                                     int n_values, int dv, int staged, int by_four) {
   extern __shared__ __align__(16) float mix_smem[];   // staged: the token's rows of `wide`, then the mixing table
   pdl_launch_dependents();
   pdl_wait();
@@ -301,9 +323,44 @@ __global__ void head_mix_gate_kernel(const float* __restrict__ wide, const float
     __syncthreads();
     rows = mix_smem;
   }
+  const int group = n_q / n_kv;
+  if (by_four) {   // four columns of one head a thread: vector loads and stores, the index arithmetic once for four
+    for (int e = threadIdx.x * 4; e < width; e += blockDim.x * 4) {
+      const int h = e / dv, d = e % dv;
+      const int slot = n_values > 1 ? h / group : 0;
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      if (mix) {
+        for (int g = 0; g < n_q; ++g) {
+          const float m = table[h * n_q + g];
+          const float4 r = *reinterpret_cast<const float4*>(rows + ((size_t)g * n_values + slot) * dv + d);
+          sum[0] = fmaf(m, r.x, sum[0]); sum[1] = fmaf(m, r.y, sum[1]);
+          sum[2] = fmaf(m, r.z, sum[2]); sum[3] = fmaf(m, r.w, sum[3]);
+        }
+      } else {
+        const float4 r = *reinterpret_cast<const float4*>(rows + ((size_t)h * n_values + slot) * dv + d);
+        sum[0] = r.x; sum[1] = r.y; sum[2] = r.z; sum[3] = r.w;
+      }
+      if (gate_proj) {
+        float z[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int p = 0; p < n_partials; ++p) {
+          float a[4];
+          scored_load4<TI>(gate_proj + (size_t)p * partial_stride + (size_t)t * ld + e, a);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) z[k] += a[k];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (gate_bias) z[k] += gate_bias[e + k];
+          sum[k] *= 1.0f / (1.0f + expf(-z[k]));
+        }
+      }
+      scored_store4<TO>(out + (size_t)t * width + e, sum);
+    }
+    return;
+  }
   for (int e = threadIdx.x; e < width; e += blockDim.x) {
     const int h = e / dv, d = e % dv;
-    const int slot = n_values > 1 ? h / (n_q / n_kv) : 0;
+    const int slot = n_values > 1 ? h / group : 0;
     float sum;
     if (mix) {
       sum = 0.f;
@@ -424,10 +481,13 @@ extern "C" int lse_head_mix_gate(const float* wide, const float* mix, const void
   const int threads = n_q * dv >= 1024 ? 256 : 128;
   const size_t row_bytes = sizeof(float) * ((size_t)n_q * n_values * dv + (size_t)n_q * n_q);
   const int staged = mix != nullptr && row_bytes <= 48 * 1024 && (n_q * n_values * dv) % 4 == 0 && (((uintptr_t)wide) & 15) == 0;
+  const int gate_bytes = gate_dtype == LSE_DTYPE_F32 ? 4 : 2;
+  const int by_four = dv % 4 == 0 && (((uintptr_t)wide | (uintptr_t)out) & 15) == 0 &&
+                      (!gate_proj || ((((uintptr_t)gate_proj) & (4 * gate_bytes - 1)) == 0 && ld % 4 == 0 && partial_stride % 4 == 0));
 #define LSE_MIX_CASE(TI, TO)                                                                                        \
   lse_launch(head_mix_gate_kernel<TI, TO>, tokens, threads, staged ? row_bytes : 0, stream, wide, mix,              \
              (const TI*)gate_proj, n_partials, partial_stride, ld, gate_bias, segment_of_token, (TO*)out, n_q, n_kv,  \
-             n_values, dv, staged)
+             n_values, dv, staged, by_four)
   if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_MIX_CASE(float, float);
   else if (gate_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_MIX_CASE(__nv_bfloat16, __nv_bfloat16);
   else if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_MIX_CASE(float, __nv_bfloat16);

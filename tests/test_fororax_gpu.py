@@ -58,7 +58,9 @@ CONFIGS = {
                         attention2(heads=18, kv_heads=2, dim=10, vdim=6, mlp=moe(experts=7, identity=1, top=4, ff=18, shared=(10, 0.5))),
                         attention(heads=9, kv_heads=1, dim=12, vdim=28, mlp=moe(experts=3, identity=5, top=3, ff=50, limit=0.3)),
                         attention(heads=5, kv_heads=1, dim=12, vdim=28, kv_from=2, mlp=None),
-                        attention2(heads=2, kv_heads=2, dim=36, vdim=20)], width=102, vocab=333, positions=900),
+                        attention2(heads=2, kv_heads=2, dim=36, vdim=20),
+                        # a reader of the pages of a layer with biases, sink and mixing (their keys carry the bias)
+                        attention(heads=4, kv_heads=2, dim=10, vdim=6, kv_from=1, mlp=None)], width=102, vocab=333, positions=900),
 }
 RMS_LIMIT = {"float32": 2.0e-5, "bfloat16": 1.0e-1}
 _MODELS: dict = {}
