@@ -767,7 +767,7 @@ def fororax_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflo
         "work_gflop_a_layer": round(moe_flops / 1e9, 1), "note": "library kernels: see the kernel table for their time"}
     out["prefill"]["qwen2 feed-forward products (library)"] = {"work_gflop_a_layer": round(dense_flops / 1e9, 1)}
     out["prefill"]["fororax rows of the mixture (route, place, gather, activation, combine)"] = frac(
-        f["prefill_kernels"], ("moe_",), 6, tokens * width * 2 * (1 + 2 * top) + tokens * top * expert_ff * 2 * 3 + tokens * width * 4 * 2, 0, fma)
+        f["prefill_kernels"], ("moe_",), 6, tokens * width * 2 * (1 + 2 * top) + tokens * (top * expert_ff + shared_ff) * 2 * 3 + tokens * width * 4 * 2, 0, fma)
     out["prefill"]["fororax scaled_add_rmsnorm"] = frac(
         f["prefill_kernels"], "scaled_add_rmsnorm", 12, tokens * width * (4 * 2 + 4 + 2), 0, fma)
     out["prefill"]["fororax head_norm_kv_write"] = frac(

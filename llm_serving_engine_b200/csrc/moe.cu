@@ -120,10 +120,11 @@ template <typename TI, typename TO>
 __global__ void moe_gated_act8_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
                                       const float* __restrict__ expert_weights, const float* __restrict__ shared_gate,
                                       TO* __restrict__ out, int experts, int ff, int shared_ff, float limit,
-                                      float shared_limit) {
+                                      float shared_limit, const int* __restrict__ valid_rows) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  if (valid_rows && t >= *valid_rows) return;   // rows behind the last expert's range of a grouped buffer
   const int inter = experts * ff + shared_ff;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (i >= inter) return;
@@ -155,7 +156,9 @@ __global__ void moe_gated_act8_kernel(const TI* __restrict__ gate_up, int n_part
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     const float gc = fminf(g[e], lim), uc = fminf(fmaxf(u[e], -lim), lim);
-    y[e] = c * (gc / (1.0f + expf(-1.702f * gc)) * (uc + 1.0f));
+    // the result is rounded to bfloat16 far more coarsely than the fast exponential and division err
+    const float gated = sizeof(TO) == 2 ? __fdividef(gc, 1.0f + __expf(-1.702f * gc)) : gc / (1.0f + expf(-1.702f * gc));
+    y[e] = c * (gated * (uc + 1.0f));
   }
   moe_store8<TO>(dst, y);
 }
@@ -310,7 +313,7 @@ extern "C" int lse_moe_route(const float* logits, int n_partials, long long part
 extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
                                  const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
                                  int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,
-                                 cudaStream_t stream) {
+                                 const int* valid_rows, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int inter = experts * ff + shared_ff;
   if (inter <= 0 || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
@@ -321,7 +324,7 @@ extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partia
 #define LSE_MOE_ACT_CASE(TI, TO)                                                                                      \
   if (wide)                                                                                                           \
     lse_launch(moe_gated_act8_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)gate_up, n_partials, partial_stride, \
-               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit);                   \
+               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit, valid_rows);       \
   else                                                                                                                \
     lse_launch(moe_gated_act_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)gate_up, n_partials, partial_stride,  \
                expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit)

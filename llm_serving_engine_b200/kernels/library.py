@@ -86,7 +86,7 @@ _SIGNATURES = {
     "lse_moe_route": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                       c_int, c_int, c_int, c_void_p],
     "lse_moe_gated_act": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                          c_int, c_float, c_float, c_void_p],
+                          c_int, c_float, c_float, c_void_p, c_void_p],
     "lse_moe_group_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lse_moe_gather_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "lse_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

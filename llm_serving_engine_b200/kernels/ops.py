@@ -925,13 +925,15 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, outputs: in
 
 
 def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_gate: torch.Tensor | None,
-                  out: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float) -> torch.Tensor:
+                  out: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float,
+                  valid_rows: torch.Tensor | None = None) -> torch.Tensor:
     """out[t, i] = c * g * sigmoid(1.702 g) * (u + 1) with g = min(gate_i, limit), u = clamp(up_i, -limit, limit), over
     the columns of all experts side by side (``experts`` blocks of ``ff``, then ``shared_ff`` of the shared expert with
     its own limit); c is the token's weight of the column's expert (``shared_gate`` for the shared columns; 1 where
     the weights are None).  ``gate_up`` is [T, 2 I] (expert by expert [gate | up], then the shared expert's
-    [gate | up]) or a float32 stack of partial sums."""
-    _need_cuda(gate_up, expert_weights, shared_gate, out)
+    [gate | up]) or a float32 stack of partial sums.  ``valid_rows`` (int32, one number on the device): rows from it on
+    may be left alone (the unused end of a buffer grouped by expert)."""
+    _need_cuda(gate_up, expert_weights, shared_gate, out, valid_rows)
     tokens, inter = out.shape
     assert inter == experts * ff + shared_ff and out.is_contiguous() and gate_up.shape[-1] == 2 * inter
     gate_up, n_partials, stride = _partials(gate_up, tokens, 2 * inter)
@@ -940,7 +942,7 @@ def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_ga
     check(library.load().lse_moe_gated_act(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride,
                                            _ptr(expert_weights), _ptr(shared_gate), out.data_ptr(),
                                            dtype_code(out.dtype), tokens, experts, ff, shared_ff, float(limit),
-                                           float(shared_limit), _stream()), "moe_gated_act")
+                                           float(shared_limit), _ptr(valid_rows), _stream()), "moe_gated_act")
     return out
 
 

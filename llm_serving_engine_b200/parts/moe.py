@@ -114,7 +114,7 @@ class ClampedMoE(FeedForward):
         ops.moe_gather_rows(x, row_of, grouped)
         gate_up = torch._grouped_mm(grouped, self._grouped_gate_up, offs=offsets)     # rows beyond the last range stay as they are
         act = torch.empty((rows, self.ff), dtype=x.dtype, device=x.device)
-        ops.moe_gated_act(gate_up, None, None, act, 1, self.ff, 0, self.limit, 0.0)
+        ops.moe_gated_act(gate_up, None, None, act, 1, self.ff, 0, self.limit, 0.0, valid_rows=offsets[-1:])
         down = torch._grouped_mm(act, self._grouped_down, offs=offsets)
         out = y if y is not None else torch.empty((tokens, width), dtype=torch.float32, device=x.device)
         return ops.moe_combine(down, row_of, chosen, expert_weights, identity_weight if self.identity else None, x, out,
