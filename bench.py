@@ -756,8 +756,8 @@ def fororax_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflo
     # attention: 3 layers of each kind; attention_2 takes Q K^T and P V once per key/value head's values
     qkv_bytes = tokens * (heads + 2 * kv_heads) * 128 * 2 * 2
     work = 4 * pairs * heads * 128
-    out["prefill"]["fororax attention (mma.sync; 3 layers with the penalty, 3 with sink and all groups' values)"] = frac(
-        f["prefill_kernels"], "attention_scored_mma", 3 + 3 * kv_heads, qkv_bytes, work, tensor)
+    out["prefill"]["fororax attention (tcgen05; 3 layers with the penalty, 3 with sink and all groups' values)"] = frac(
+        f["prefill_kernels"], ("attention_scored_mma", "attn_prefill_tc"), 3 + 3 * kv_heads, qkv_bytes, work, tensor)
     out["prefill"]["qwen2 attention (tcgen05)"] = frac(q["prefill_kernels"], "attn_", 6, qkv_bytes, work, tensor)
     # feed-forward products: Qwen2's are library products of [tokens, width] x [3 ff, width]; the mixture's are the
     # grouped products over the chosen experts' rows and the shared expert's plain products

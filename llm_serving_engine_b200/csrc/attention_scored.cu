@@ -287,8 +287,9 @@ template <> __device__ __forceinline__ void scored_store4<__nv_bfloat16>(__nv_bf
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename TI, typename TO>
-__global__ void head_mix_gate_kernel(const float* __restrict__ wide, const float* __restrict__ mix,
+// TW: the type of `wide` (float32, or bfloat16 from a kernel that writes its outputs rounded; then the rows are staged).
+template <typename TI, typename TO, typename TW>
+__global__ void head_mix_gate_kernel(const TW* __restrict__ wide, const float* __restrict__ mix,
                                      const TI* __restrict__ gate_proj, int n_partials, long long partial_stride,
                                      long long ld, const float* __restrict__ gate_bias,
                                      const int* __restrict__ segment_of_token, TO* __restrict__ out, int n_q, int n_kv,
@@ -300,20 +301,20 @@ __global__ void head_mix_gate_kernel(const float* __restrict__ wide, const float
   if (segment_of_token[t] < 0) return;
   const int width = n_q * dv;
   const int row_floats = n_q * n_values * dv;
-  const float* rows = wide + (size_t)t * row_floats;
+  const float* rows = sizeof(TW) == 4 ? reinterpret_cast<const float*>(wide) + (size_t)t * row_floats : nullptr;
   const float* table = mix;
-  if (staged) {   // every output reads n_q of the rows: fetched once, four floats a load, all loads of a thread in flight
-    const float4* src = reinterpret_cast<const float4*>(rows);
+  if (staged) {   // every output reads n_q of the rows: fetched once, four values a load, all loads of a thread in flight
+    const TW* src = wide + (size_t)t * row_floats;
     float4* dst = reinterpret_cast<float4*>(mix_smem);
     const int pieces = row_floats / 4;
     for (int base = threadIdx.x; base < pieces; base += 4 * blockDim.x) {
-      float4 v[4];
+      float v[4][4];
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (base + k * blockDim.x < pieces) v[k] = src[base + k * blockDim.x];
+        if (base + k * blockDim.x < pieces) scored_load4<TW>(src + 4 * (size_t)(base + k * blockDim.x), v[k]);
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        if (base + k * blockDim.x < pieces) dst[base + k * blockDim.x] = v[k];
+        if (base + k * blockDim.x < pieces) dst[base + k * blockDim.x] = make_float4(v[k][0], v[k][1], v[k][2], v[k][3]);
     }
     if (mix) {
       float* held = mix_smem + row_floats;
@@ -469,9 +470,16 @@ extern "C" int lse_attention_scored_merge(const float* partials, void* out, int 
   LSE_LAUNCH_CHECK();
 }
 
-// wide float32 [T, n_q, n_values, dv] (n_values = n_kv when cross, else 1); mix float32 [n_q, n_q] or null;
+// wide [T, n_q, n_values, dv] (n_values = n_kv when cross, else 1) in float32, or in bfloat16 (wide_bf16; only shapes
+// whose rows fit the kernel's shared memory, see lse_head_mix_gate_stages); mix float32 [n_q, n_q] or null;
 // gate_proj [T, ld] (columns from the pointer on) or a float32 stack of partial sums, or null; out [T, n_q * dv].
-extern "C" int lse_head_mix_gate(const float* wide, const float* mix, const void* gate_proj, int gate_dtype,
+constexpr size_t MIX_STAGE_BYTES = 160 * 1024;   // most shared memory that the mixing kernel stages a token's rows in
+
+extern "C" int lse_head_mix_gate_stages(int n_q, int n_values, int dv) {
+  return sizeof(float) * ((size_t)n_q * n_values * dv + (size_t)n_q * n_q) <= MIX_STAGE_BYTES && (n_q * n_values * dv) % 4 == 0;
+}
+
+extern "C" int lse_head_mix_gate(const void* wide, int wide_bf16, const float* mix, const void* gate_proj, int gate_dtype,
                                  int n_partials, long long partial_stride, long long ld, const float* gate_bias,
                                  const int* segment_of_token, void* out, int out_dtype, int tokens, int n_q, int n_kv,
                                  int cross, int dv, cudaStream_t stream) {
@@ -480,18 +488,36 @@ extern "C" int lse_head_mix_gate(const float* wide, const float* mix, const void
   const int n_values = cross ? n_kv : 1;
   const int threads = n_q * dv >= 1024 ? 256 : 128;
   const size_t row_bytes = sizeof(float) * ((size_t)n_q * n_values * dv + (size_t)n_q * n_q);
-  const int staged = mix != nullptr && row_bytes <= 48 * 1024 && (n_q * n_values * dv) % 4 == 0 && (((uintptr_t)wide) & 15) == 0;
+  const int staged = (mix != nullptr || wide_bf16) && lse_head_mix_gate_stages(n_q, n_values, dv) && (((uintptr_t)wide) & 15) == 0;
+  if (wide_bf16 && !staged) return LSE_ERR_BAD_ARGUMENT;
   const int gate_bytes = gate_dtype == LSE_DTYPE_F32 ? 4 : 2;
   const int by_four = dv % 4 == 0 && (((uintptr_t)wide | (uintptr_t)out) & 15) == 0 &&
                       (!gate_proj || ((((uintptr_t)gate_proj) & (4 * gate_bytes - 1)) == 0 && ld % 4 == 0 && partial_stride % 4 == 0));
+#define LSE_MIX_CONFIGURE(kernel)                                                                                   \
+  {                                                                                                                 \
+    static bool configured = false;   /* once per instantiation, never while a stream is captured (a first run comes first) */ \
+    if (!configured && staged && row_bytes > 48 * 1024) {                                                           \
+      const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MIX_STAGE_BYTES); \
+      if (err != cudaSuccess) return (int)err;                                                                      \
+      configured = true;                                                                                            \
+    }                                                                                                               \
+  }
 #define LSE_MIX_CASE(TI, TO)                                                                                        \
-  lse_launch(head_mix_gate_kernel<TI, TO>, tokens, threads, staged ? row_bytes : 0, stream, wide, mix,              \
-             (const TI*)gate_proj, n_partials, partial_stride, ld, gate_bias, segment_of_token, (TO*)out, n_q, n_kv,  \
-             n_values, dv, staged, by_four)
-  if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_MIX_CASE(float, float);
-  else if (gate_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_MIX_CASE(__nv_bfloat16, __nv_bfloat16);
-  else if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_MIX_CASE(float, __nv_bfloat16);
+  LSE_MIX_CONFIGURE((head_mix_gate_kernel<TI, TO, __nv_bfloat16>))                                                  \
+  LSE_MIX_CONFIGURE((head_mix_gate_kernel<TI, TO, float>))                                                          \
+  if (wide_bf16)                                                                                                    \
+    lse_launch(head_mix_gate_kernel<TI, TO, __nv_bfloat16>, tokens, threads, row_bytes, stream,                     \
+               (const __nv_bfloat16*)wide, mix, (const TI*)gate_proj, n_partials, partial_stride, ld, gate_bias,     \
+               segment_of_token, (TO*)out, n_q, n_kv, n_values, dv, staged, by_four);                               \
+  else                                                                                                              \
+    lse_launch(head_mix_gate_kernel<TI, TO, float>, tokens, threads, staged ? row_bytes : 0, stream,                \
+               (const float*)wide, mix, (const TI*)gate_proj, n_partials, partial_stride, ld, gate_bias,            \
+               segment_of_token, (TO*)out, n_q, n_kv, n_values, dv, staged, by_four)
+  if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_MIX_CASE(float, float); }
+  else if (gate_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_MIX_CASE(__nv_bfloat16, __nv_bfloat16); }
+  else if (gate_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_MIX_CASE(float, __nv_bfloat16); }
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_MIX_CASE
+#undef LSE_MIX_CONFIGURE
   LSE_LAUNCH_CHECK();
 }

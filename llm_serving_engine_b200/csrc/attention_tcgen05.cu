@@ -90,14 +90,19 @@ constexpr size_t attn_tc_smem() {
   return 1024 + (size_t)(D / 64) * HALF_BYTES * (1 + 2 * GROUPS) + (size_t)GROUPS * 2 * HALF_BYTES + 256;
 }
 
-template <int D>
+// PEN: a distance penalty r1_h log2(1 + r2_h (i - j)) is taken off the scores (in base two).  sink (or null): exp(sink_h)
+// joins the softmax's denominator.  n_values > 1: blockIdx.y is the key/value head whose VALUES the block applies its
+// head's weights to (the keys are always the head's own), and the output has a slot per value head:
+// out[((row * n_q + head) * n_values + slot) * D].
+template <int D, bool PEN>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                        const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ segment_start,
                        const int* __restrict__ segment_first_pos, int num_segments, int n_q, int n_kv, int page_size,
                        float scale_log2e, int num_pages, int skip_single, int parts, float* __restrict__ scratch,
-                       int* __restrict__ counters) {
+                       int* __restrict__ counters, const float* __restrict__ r1, const float* __restrict__ r2,
+                       const float* __restrict__ sink, int n_values) {
   constexpr int HALVES = D / 64;
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = 2 * HALF_BYTES;
   constexpr uint32_t GROUP_BYTES = HALVES * 1024;   // 8 keys (or values) in a stage: 8 rows x 128 bytes for every 64 columns
@@ -122,6 +127,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int part = (int)(blockIdx.x / n_q) % parts;
   const int rank = (int)(blockIdx.x / n_q) / parts;
   const int kvh = head / (n_q / n_kv);
+  const int value_slot = blockIdx.y;
+  const int value_head = n_values > 1 ? value_slot : kvh;
   pdl_launch_dependents();
 
   // which tile of which request (the step's own data: read before waiting for the kernels before);
@@ -147,7 +154,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (part >= sharing) return;
   const int j_lo = (int)((long long)part * n_tiles / sharing);
   const int n_local = (int)((long long)(part + 1) * n_tiles / sharing) - j_lo;
-  const int slot = rank * n_q + head;
+  const int slot = (value_slot * (int)(gridDim.x / (unsigned)parts / (unsigned)n_q) + rank) * n_q + head;
 #ifdef LSE_TRACE
   const bool traced = seg == 0 && head == 0 && r0 + BM >= cnt && (tid == 0 || tid == GROUP_THREADS || tid == MMA_WARP * 32 || tid == PV_WARP * 32);
 #endif
@@ -181,7 +188,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const int j = j_lo + jj;
       return (jj < n_local && lane < min(ppt, n_pages - j * ppt)) ? LSE_CHECKED(bt[j * ppt + lane], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY) : 0;
     };
-    auto load = [&](int jj, int page, uint32_t dst, const CUtensorMap* map, int full, int empty) -> bool {
+    auto load = [&](int jj, int page, uint32_t dst, const CUtensorMap* map, int full, int empty, int cache_head) -> bool {
       const int g = jj & 1;
       const uint32_t parity = (uint32_t)(jj >> 1) & 1u;
       const int np = min(ppt, n_pages - (j_lo + jj) * ppt);
@@ -192,15 +199,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __syncwarp();
       if (lane < np)   // one copy per page: its groups of 8 keys, the two halves of the head size side by side
         tma_load_4d(dst + g * KV_BYTES + (uint32_t)(lane * page_size) * 128u * HALVES, map, bar(full + g), 0, 0, 0,
-                    (page * n_kv + kvh) * (page_size / 8));
+                    (page * n_kv + cache_head) * (page_size / 8));
       return true;
     };
     int page_k = page_of(0), page_v = page_k;
-    bool ok = load(0, page_k, k_s, &map_k, B_KF, B_KE);
+    bool ok = load(0, page_k, k_s, &map_k, B_KF, B_KE, kvh);
     for (int jj = 0; jj < n_local && ok; ++jj) {
       page_k = page_of(jj + 1);
-      if (jj + 1 < n_local) ok = load(jj + 1, page_k, k_s, &map_k, B_KF, B_KE);
-      if (ok) ok = load(jj, page_v, v_s, &map_v, B_VF, B_VE);
+      if (jj + 1 < n_local) ok = load(jj + 1, page_k, k_s, &map_k, B_KF, B_KE, kvh);
+      if (ok) ok = load(jj, page_v, v_s, &map_v, B_VF, B_VE, value_head);
       page_v = page_k;
     }
   } else if (warp == MMA_WARP) {
@@ -273,6 +280,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int my_pos = pos0 + min(row, nrows - 1);
     unsigned char* prow = gbase + (p_s - base) + g * P_BYTES + row * 128;
     float m_used = -INFINITY, m_seen = -INFINITY, l = 0.f;   // the maximum that O and l are relative to; the largest score seen
+    const float pen1 = PEN ? r1[head] : 0.f, pen2 = PEN ? r2[head] : 0.f;
+    // the penalty of key `key` for this thread's row, in base two (hidden keys, beyond the row's position, get none)
+    // (Reading it from a table of all distances worked out ahead was measured no faster: what the penalty costs is
+    // the softmax threads' issue slots and registers, not the logarithm.)
+    // `ahead`: how far the row's position lies ahead of the key (hidden keys, at a negative distance, get no penalty)
+    auto penalty = [&](float ahead) { return pen1 * __log2f(fmaf(pen2, fmaxf(ahead, 0.f), 1.0f)); };
     bool pending = false;                                    // m_seen has outgrown m_used: O and l are to be rescaled
     // `ok` is the same in all lanes of a warp (a vote after every wait).  A warp whose wait gave up
     // still meets the warp of the other group at the pair barrier, which has no time limit of its own.
@@ -306,11 +319,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             for (int i = 0; i < 32; ++i)
               if (kv0 + c + i > my_pos) s[i] = 0xff800000u;
           }
+          if (PEN) {
+            const float ahead = (float)(my_pos - kv0 - c);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaf(__uint_as_float(s[i]), scale_log2e, -penalty(ahead - (float)i)));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(s[i]), __uint_as_float(s[i + 1])));
+          }
         }
         // a row of tile 0 always sees key 0; a row's last tile may be hidden entirely (-inf: nothing is added then)
-        m_used = m_seen = mx * scale_log2e;
+        m_used = m_seen = PEN ? mx : mx * scale_log2e;
       } else if (pending) {   // the tile before raised the maximum by more than the step: O and the sum follow now
         rescale = true;
         alpha = m_used == -INFINITY ? 0.f : exp2_fast(m_used - m_seen);
@@ -355,13 +374,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
               if (kv0 + c + i > my_pos) s[i] = 0xff800000u;
           }
           uint32_t pk[16];
+          const float ahead_of_chunk = (float)(my_pos - kv0 - c);
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
-            const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
-            const float s2 = __uint_as_float(s[2 * i + 2]), s3 = __uint_as_float(s[2 * i + 3]);
+            float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
+            float s2 = __uint_as_float(s[2 * i + 2]), s3 = __uint_as_float(s[2 * i + 3]);
+            float p0, p1, p2, p3;
+            if (PEN) {   // scaled and penalised first: the maximum is taken over what is exponentiated
+              const float ahead = ahead_of_chunk - (float)(2 * i);
+              s0 = fmaf(s0, scale_log2e, -penalty(ahead)); s1 = fmaf(s1, scale_log2e, -penalty(ahead - 1.0f));
+              s2 = fmaf(s2, scale_log2e, -penalty(ahead - 2.0f)); s3 = fmaf(s3, scale_log2e, -penalty(ahead - 3.0f));
+              p0 = s0 + neg; p1 = s1 + neg; p2 = s2 + neg; p3 = s3 + neg;
+            } else {
+              p0 = fmaf(s0, scale_log2e, neg); p1 = fmaf(s1, scale_log2e, neg);
+              p2 = fmaf(s2, scale_log2e, neg); p3 = fmaf(s3, scale_log2e, neg);
+            }
             mx = fmaxf(mx, fmaxf(fmaxf(s0, s1), fmaxf(s2, s3)));
-            float p0 = fmaf(s0, scale_log2e, neg), p1 = fmaf(s1, scale_log2e, neg);
-            float p2 = fmaf(s2, scale_log2e, neg), p3 = fmaf(s3, scale_log2e, neg);
             p0 = exp2_fast(p0); p1 = exp2_fast(p1); p2 = exp2_fast(p2); p3 = exp2_fast(p3);
             sum += (p0 + p1) + (p2 + p3);
             pk[i] = pack_bf16(p0, p1);
@@ -385,7 +413,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (c + 64 < BN) tmem_ld32(s_addr + c + 64, sa);
           take(sb, c + 32);
         }
-        const float m_tile = mx * scale_log2e;
+        const float m_tile = PEN ? mx : mx * scale_log2e;
         if (first || !__any_sync(0xffffffffu, m_tile > m_used + REDO_STEP)) {
           l += sum;
           m_seen = fmaxf(m_seen, m_tile);
@@ -434,14 +462,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // a block that holds all keys of its rows divides by the sum here; one that holds a part of them leaves its
     // output relative to its own maximum, undivided
     const bool shared = sharing > 1;
-    const float inv = shared ? 1.0f : 1.0f / l_all;
+    float inv = 1.0f;
+    if (!shared) {
+      inv = 1.0f / l_all;
+      if (sink) {   // exp(sink) joins the sum; the outputs are rescaled when the sink is the new maximum
+        const float sink2 = sink[head] * LOG2E;
+        const float m_fin = fmaxf(m_all, sink2);
+        const float w_rows = exp2_fast(m_all - m_fin);
+        inv = w_rows / fmaf(l_all, w_rows, exp2_fast(sink2 - m_fin));
+      }
+    }
     const float w0 = (g == 0 ? w_mine : w_other) * inv, w1 = (g == 0 ? w_other : w_mine) * inv;
     // both groups' last products must have landed (group 1 has none when there is a single tile)
     const int n0 = (n_local + 1) / 2, n1 = n_local / 2;
     if (ok) ok = wait_all(B_OD + 0, (uint32_t)(n0 - 1) & 1u);
     if (ok && n1 > 0) ok = wait_all(B_OD + 1, (uint32_t)(n1 - 1) & 1u);
     // this thread owns columns g * D/2 .. of its row: the same columns of both groups' outputs
-    __nv_bfloat16* dst = out + ((size_t)(row_base + row) * n_q + head) * D + g * OD;
+    __nv_bfloat16* dst = out + (((size_t)(row_base + row) * n_q + head) * n_values + value_slot) * D + g * OD;
     if (!shared) {
       if (ok) {
         fence_after_sync();
@@ -511,12 +548,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           m_parts[p] = p < sharing ? __ldcg(parts_base + (size_t)p * PART_FLOATS + BM * D + row) : -INFINITY;
           m_tile = fmaxf(m_tile, m_parts[p]);
         }
+        const float sink2 = sink ? sink[head] * LOG2E : -INFINITY;
+        m_tile = fmaxf(m_tile, sink2);
         float sum = 0.f, weight[MAX_PARTS];
 #pragma unroll
         for (int p = 0; p < MAX_PARTS; ++p) {
           weight[p] = (p < sharing && m_parts[p] != -INFINITY) ? exp2_fast(m_parts[p] - m_tile) : 0.f;
           if (p < sharing) sum = fmaf(__ldcg(parts_base + (size_t)p * PART_FLOATS + BM * D + BM + row), weight[p], sum);
         }
+        if (sink) sum += exp2_fast(sink2 - m_tile);
         const float inv_sum = 1.0f / sum;
         if (row < nrows) {
 #pragma unroll 2
@@ -553,15 +593,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #endif
 }
 
-template <int D>
+template <int D, bool PEN>
 int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, const int* block_tables, int bt_stride,
                       const int* segment_start, const int* segment_first_pos, int num_segments, int tokens,
                       long long num_pages, int n_q, int n_kv, int page_size, float scale, int skip_single,
-                      int max_portions, float* scratch, int* counters, long long scratch_slots, cudaStream_t stream) {
+                      int max_portions, float* scratch, int* counters, long long scratch_slots, const float* r1,
+                      const float* r2, const float* sink, int n_values, cudaStream_t stream) {
   const size_t smem = attn_tc_smem<D>();
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attn_prefill_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(attn_prefill_tc_kernel<D, PEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
@@ -584,15 +625,16 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
   }
   const long long blocks = (long long)tiles * n_q;
   int parts = 1;
-  if (scratch != nullptr && counters != nullptr && blocks <= scratch_slots) {
-    parts = (int)((5LL * sm_count) / (4 * blocks));
+  if (scratch != nullptr && counters != nullptr && blocks * n_values <= scratch_slots) {
+    parts = (int)((5LL * sm_count) / (4 * blocks * n_values));
     parts = parts < 1 ? 1 : (parts > MAX_PARTS ? MAX_PARTS : parts);
   }
-  dim3 grid((unsigned)(blocks * parts));
-  cudaError_t err = lse_launch(attn_prefill_tc_kernel<D>, grid, THREADS, smem, stream, map_q, map_k, map_v,
+  if (n_values > 65535) return LSE_ERR_TOO_LARGE;
+  dim3 grid((unsigned)(blocks * parts), (unsigned)n_values);
+  cudaError_t err = lse_launch(attn_prefill_tc_kernel<D, PEN>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
                                num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages, skip_single, parts,
-                               scratch, counters);
+                               scratch, counters, r1, r2, sink, n_values);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -650,10 +692,32 @@ extern "C" int lse_paged_attention_prefill_tc(const void* q, const void* k_cache
       (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
     return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
-    return launch_prefill_tc<128>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                                  num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, scratch,
-                                  counters, scratch_slots, stream);
-  return launch_prefill_tc<64>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
-                               num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions, scratch,
-                                  counters, scratch_slots, stream);
+    return launch_prefill_tc<128, false>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
+                                         num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions,
+                                         scratch, counters, scratch_slots, nullptr, nullptr, nullptr, 1, stream);
+  return launch_prefill_tc<64, false>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
+                                      num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions,
+                                      scratch, counters, scratch_slots, nullptr, nullptr, nullptr, 1, stream);
+}
+
+// The same kernel with learned changes to its scores or weights (see attention_scored.cu): r1, r2 (together, float32
+// [n_q], or null): the distance penalty; sink (float32 [n_q] or null); cross != 0: out is [tokens, n_q, n_kv, D] and slot
+// c of a head holds its weights applied to the values of key/value head c.  Every request's rows are worked on (single
+// tokens take a tile of their own).
+extern "C" int lse_attention_scored_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                       const int* block_tables, int bt_stride, const int* segment_start,
+                                       const int* segment_first_pos, int num_segments, int tokens, long long num_pages,
+                                       int n_q, int n_kv, int head_dim, int page_size, float scale, const float* r1,
+                                       const float* r2, const float* sink, int cross, float* scratch, int* counters,
+                                       long long scratch_slots, cudaStream_t stream) {
+  if (tokens <= 0 || num_segments <= 0) return 0;
+  if (!lse_attention_tc_supported(head_dim, n_q, n_kv, page_size) || num_pages <= 0 || !(scale > 0.f) || (!r1) != (!r2) ||
+      (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
+    return LSE_ERR_BAD_ARGUMENT;
+  const int n_values = cross ? n_kv : 1;
+#define LSE_SCORED_TC_ARGS q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos, num_segments, \
+  tokens, num_pages, n_q, n_kv, page_size, scale, 0, 0, scratch, counters, scratch_slots, r1, r2, sink, n_values, stream
+  if (head_dim == 128) return r1 ? launch_prefill_tc<128, true>(LSE_SCORED_TC_ARGS) : launch_prefill_tc<128, false>(LSE_SCORED_TC_ARGS);
+  return r1 ? launch_prefill_tc<64, true>(LSE_SCORED_TC_ARGS) : launch_prefill_tc<64, false>(LSE_SCORED_TC_ARGS);
+#undef LSE_SCORED_TC_ARGS
 }

@@ -101,8 +101,12 @@ _SIGNATURES = {
     "lse_attention_scored_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_int, c_void_p],
-    "lse_head_mix_gate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p,
+    "lse_head_mix_gate": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_head_mix_gate_stages": [c_int, c_int, c_int],
+    "lse_attention_scored_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                                c_void_p, c_void_p, c_longlong, c_void_p],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],

@@ -866,6 +866,40 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     return out
 
 
+def head_mix_gate_stages(n_q: int, n_values: int, dv: int) -> bool:
+    """Whether :func:`head_mix_gate` keeps a token's rows in shared memory at this shape (it takes bfloat16 rows only then)."""
+    return bool(library.load().lse_head_mix_gate_stages(int(n_q), int(n_values), int(dv)))
+
+
+def attention_scored_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                        block_tables: torch.Tensor, segment_start: torch.Tensor, segment_first_position: torch.Tensor,
+                        scale: float, r1: torch.Tensor | None = None, r2: torch.Tensor | None = None,
+                        sink: torch.Tensor | None = None, cross: bool = False) -> torch.Tensor:
+    """:func:`attention_scored` for prompt portions on the 5th-generation tensor cores (the kernel of
+    :func:`paged_attention_prefill_tc` with the penalty, the sink and the value head as a grid dimension): bfloat16,
+    keys and values of one size, 64 or 128, pages of 8 to 128 keys.  out [T, n_q, dv] or, with ``cross``,
+    [T, n_q, n_kv, dv], bfloat16.  Every request of the step is worked on in tiles of 128 rows."""
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position, r1, r2, sink)
+    tokens, n_q, head_dim = q.shape
+    pages, n_kv, page_size = k_cache.shape[0], k_cache.shape[1], k_cache.shape[2]
+    segments = segment_first_position.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert v_cache.shape == k_cache.shape and k_cache.shape[3] == head_dim
+    assert out.numel() == tokens * n_q * (n_kv if cross else 1) * head_dim
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and segment_start.shape[0] == segments + 1
+    for vector in (r1, r2, sink):
+        assert vector is None or (vector.dtype == torch.float32 and vector.shape == (n_q,))
+    scratch, counters = _attention_tc_scratch(q.device)
+    check(library.load().lse_attention_scored_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                                 block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
+                                                 segment_first_position.data_ptr(), segments, tokens, pages, n_q, n_kv,
+                                                 head_dim, page_size, float(scale), _ptr(r1), _ptr(r2), _ptr(sink),
+                                                 int(cross), _ptr(scratch), _ptr(counters), counters.shape[0], _stream()),
+          "attention_scored_tc")
+    return out
+
+
 def attention_scored_mma_supported(dk: int, dv: int, n_q: int, n_kv: int, dtype: torch.dtype) -> bool:
     """Whether the tensor-core form of :func:`attention_scored` takes this shape (bfloat16; keys and values of one
     size, 32, 48, 64, 96 or 128; at most 64 query heads a group)."""
@@ -877,14 +911,15 @@ def attention_scored_mma_supported(dk: int, dv: int, n_q: int, n_kv: int, dtype:
 def head_mix_gate(wide: torch.Tensor, mix: torch.Tensor | None, gate_proj: torch.Tensor | None, gate_offset: int,
                   gate_bias: torch.Tensor | None, segment_of_token: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
                   dv: int) -> torch.Tensor:
-    """out[t, h] = sigmoid(gate)[t, h] * sum_g mix[h, g] * wide[t, g, slot of h]: ``wide`` float32 [T, n_q, n_kv, dv]
-    (the output of :func:`attention_scored` with ``cross``; the slot of h is its own key/value head) or [T, n_q, dv];
+    """out[t, h] = sigmoid(gate)[t, h] * sum_g mix[h, g] * wide[t, g, slot of h]: ``wide`` [T, n_q, n_kv, dv] in float32
+    or bfloat16 (the output of :func:`attention_scored` with ``cross``; the slot of h is its own key/value head) or [T, n_q, dv];
     ``mix`` float32 [n_q, n_q] or None; the gate's pre-activation is columns ``gate_offset`` .. + n_q * dv of
     ``gate_proj`` (+ ``gate_bias`` float32 [n_q * dv]), or None for no gate; out [T, n_q * dv]."""
     _need_cuda(wide, mix, gate_proj, gate_bias, segment_of_token, out)
     tokens = out.shape[0]
     cross = wide.numel() == tokens * n_q * n_kv * dv and n_kv > 1
-    assert wide.dtype == torch.float32 and wide.is_contiguous() and wide.numel() == tokens * n_q * (n_kv if cross else 1) * dv
+    assert wide.dtype in (torch.float32, torch.bfloat16) and wide.is_contiguous()
+    assert wide.numel() == tokens * n_q * (n_kv if cross else 1) * dv
     assert out.shape == (tokens, n_q * dv) and out.is_contiguous()
     assert mix is None or (mix.dtype == torch.float32 and mix.shape == (n_q, n_q) and mix.is_contiguous())
     code, n_partials, stride, ld, pointer = dtype_code(out.dtype), 1, 0, 0, None
@@ -892,7 +927,7 @@ def head_mix_gate(wide: torch.Tensor, mix: torch.Tensor | None, gate_proj: torch
         gate_proj, code, n_partials, stride, ld = _projection(gate_proj)
         pointer = gate_proj.data_ptr() + gate_offset * gate_proj.element_size()
         assert gate_bias is None or (gate_bias.dtype == torch.float32 and gate_bias.shape == (n_q * dv,))
-    check(library.load().lse_head_mix_gate(wide.data_ptr(), _ptr(mix), pointer, code, n_partials, stride, ld,
+    check(library.load().lse_head_mix_gate(wide.data_ptr(), int(wide.dtype == torch.bfloat16), _ptr(mix), pointer, code, n_partials, stride, ld,
                                            _ptr(gate_bias) if gate_proj is not None else None, segment_of_token.data_ptr(),
                                            out.data_ptr(), dtype_code(out.dtype), tokens, n_q, n_kv, int(cross), dv,
                                            _stream()), "head_mix_gate")

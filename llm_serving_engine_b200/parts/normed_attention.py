@@ -1,12 +1,20 @@
 """Grouped-query attention with normed heads and learned changes to its scores or weights."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import Mixer, PagedKV, register_mixer
 from .linear import linear_partials
+
+# Rows of the longest portion from which a step's attention runs on the tcgen05 kernel (tiles of 128 rows of one head),
+# when the portions are also long on average; LSE_SCORED_TCGEN05=0 keeps every step on the mma.sync kernel.
+TCGEN05_MIN_ROWS = 128
+TCGEN05_MIN_ROWS_PER_REQUEST = 64
+TCGEN05 = os.environ.get("LSE_SCORED_TCGEN05", "1") != "0"
 
 _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "q_norm": "q.norm", "k_norm": "k.norm", "r1": "r1", "r2": "r2",
                   "sink": "sink", "mix": "talk", "gate": "g", "bias_suffix": ".b"}
@@ -28,7 +36,8 @@ class NormedAttention(Mixer):
     and ``tensor_names``.  Queries and keys are RMS-normed per head with one weight [dim] shared by the heads; there
     is no rotation: positions enter through the distance penalty or not at all.
 
-    Shapes that the tensor-core kernel takes (bfloat16, keys and values of one size that is 32, 48, 64, 96 or 128) run
+    Prompt steps with a portion of 128 rows and more, heads of 64 or 128, run on the tcgen05 kernel
+    (``ops.attention_scored_tc``).  Other shapes that the mma.sync kernel takes (bfloat16, keys and values of one size that is 32, 48, 64, 96 or 128) run
     there, prompt portions as tiles of rows and few rows with their keys split into chunks; the rest, and float32, on
     the general kernel.
 
@@ -102,6 +111,20 @@ class NormedAttention(Mixer):
         dk, dv = int(params["dim"]), int(params["vdim"])
         return PagedKV(int(params["kv_heads"]), dk, 0, 0 if dv == dk else dv)
 
+    def _on_tcgen05(self, segment_counts: list[int], page_size: int | None = None) -> bool:
+        """Whether a step of this shape takes the tcgen05 kernel: bfloat16, heads of 64 or 128 (keys and values alike), a
+        portion of at least 128 rows, portions long on average (a single token would take a tile of 128 rows)."""
+        if not TCGEN05 or self.ctx.dtype != torch.bfloat16 or self.dk != self.dv or self.dk not in (64, 128):
+            return False
+        if max(segment_counts) < TCGEN05_MIN_ROWS or sum(segment_counts) < TCGEN05_MIN_ROWS_PER_REQUEST * len(segment_counts):
+            return False
+        if self.mix is not None and self.n_kv > 1 and not ops.head_mix_gate_stages(self.n_q, self.n_kv, self.dv):
+            return False
+        return page_size is None or ops.attention_tc_supported(self.dk, self.n_q, self.n_kv, page_size, self.ctx.dtype)
+
+    def launch_signature(self, segment_counts):
+        return ("tcgen05",) if self._on_tcgen05(segment_counts) else ()
+
     def forward(self, x, step, cache):
         tokens = x.shape[0]
         proj = linear_partials(x, self.in_weight)
@@ -109,16 +132,28 @@ class NormedAttention(Mixer):
         ops.head_norm_kv_write(proj, self.in_bias, self.q_norm, self.k_norm, self.eps, cache.slot_mapping, q,
                                cache.keys, cache.values, self.n_q, self.n_kv if self.own_cache else 0, self.dk, self.dv)
         attended = torch.empty((tokens, self.n_q * self.dv), dtype=x.dtype, device=x.device)
+        tcgen05 = (not step.decode_only and step.segments
+                   and self._on_tcgen05([segment.count for segment in step.segments], cache.keys.shape[2]))
         if self.mix is None and self.gate_offset < 0:
-            ops.attention_scored(q, cache.keys, cache.values, attended.view(tokens, self.n_q, self.dv), cache.block_tables,
-                                 step.segment_of_token, step.positions, self.scale, self.r1, self.r2, self.sink,
-                                 segment_start=step.segment_start, segment_first_position=step.segment_first_position)
+            if tcgen05:
+                ops.attention_scored_tc(q, cache.keys, cache.values, attended.view(tokens, self.n_q, self.dv),
+                                        cache.block_tables, step.segment_start, step.segment_first_position, self.scale,
+                                        self.r1, self.r2, self.sink)
+            else:
+                ops.attention_scored(q, cache.keys, cache.values, attended.view(tokens, self.n_q, self.dv), cache.block_tables,
+                                     step.segment_of_token, step.positions, self.scale, self.r1, self.r2, self.sink,
+                                     segment_start=step.segment_start, segment_first_position=step.segment_first_position)
         else:
             cross = self.mix is not None and self.n_kv > 1
-            wide = torch.empty((tokens, self.n_q, self.n_kv if cross else 1, self.dv), dtype=torch.float32, device=x.device)
-            ops.attention_scored(q, cache.keys, cache.values, wide, cache.block_tables, step.segment_of_token,
-                                 step.positions, self.scale, self.r1, self.r2, self.sink, cross=cross,
-                                 segment_start=step.segment_start, segment_first_position=step.segment_first_position)
+            wide = torch.empty((tokens, self.n_q, self.n_kv if cross else 1, self.dv),
+                               dtype=torch.bfloat16 if tcgen05 else torch.float32, device=x.device)
+            if tcgen05:
+                ops.attention_scored_tc(q, cache.keys, cache.values, wide, cache.block_tables, step.segment_start,
+                                        step.segment_first_position, self.scale, self.r1, self.r2, self.sink, cross=cross)
+            else:
+                ops.attention_scored(q, cache.keys, cache.values, wide, cache.block_tables, step.segment_of_token,
+                                     step.positions, self.scale, self.r1, self.r2, self.sink, cross=cross,
+                                     segment_start=step.segment_start, segment_first_position=step.segment_first_position)
             gate_bias = None
             if self.gate_offset >= 0 and self.in_bias is not None and self.in_bias.shape[0] > self.gate_offset:
                 gate_bias = self.in_bias[self.gate_offset:]

@@ -571,3 +571,65 @@ def test_rows_grouped_by_expert_have_places_of_their_own():
     for e in range(experts):
         rows = row_of[:-5][live == e]
         assert bool(((rows >= firsts[e]) & (rows < firsts[e] + counts[e])).all())
+
+
+def test_tcgen05_attention_against_the_general_kernel():
+    """Prompt portions of several requests (one from position 0, one behind a long prefix, one of a single token, one
+    that ends inside a tile), pages scattered, heads of 64 and 128 in groups of one, two and eight, with the penalty,
+    the sink and the values of every group: the tcgen05 kernel against the float32-arithmetic kernel on the same
+    bfloat16 inputs, and one far key that must be found."""
+    from llm_serving_engine_b200.kernels import ops
+    import numpy as np
+
+    torch.manual_seed(11)
+    page = 16
+    for heads, groups, size in ((4, 2, 64), (8, 1, 128), (3, 3, 128)):
+        counts, firsts = [300, 1, 129, 140], [0, 77, 500, 1000]
+        contexts = [first + count for first, count in zip(firsts, counts)]
+        pages_each = [-(-context // page) for context in contexts]
+        pool_pages = sum(pages_each) + 3
+        k_cache = (torch.randn(pool_pages, groups, page, size) * 0.5).to(torch.bfloat16).cuda()
+        v_cache = torch.randn(pool_pages, groups, page, size).to(torch.bfloat16).cuda()
+        order = torch.randperm(pool_pages).to(torch.int32)
+        table = torch.full((len(counts), max(pages_each)), -1, dtype=torch.int32)
+        cursor = 0
+        for index, count in enumerate(pages_each):
+            table[index, :count] = order[cursor:cursor + count]
+            cursor += count
+        total = sum(counts)
+        q = (torch.randn(total, heads, size) * 0.5).to(torch.bfloat16)
+        k_cache[int(table[3, 1]), groups - 1, 3] = (q[total - 5, heads - 1] * 4.0).cuda()   # key 19 of the last request, far back
+        starts = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int32).cuda()
+        seg = torch.cat([torch.full((count,), index, dtype=torch.int32) for index, count in enumerate(counts)]).cuda()
+        pos = torch.cat([torch.arange(first, first + count, dtype=torch.int32) for first, count in zip(firsts, counts)]).cuda()
+        first_pos = torch.tensor(firsts, dtype=torch.int32).cuda()
+        sink = torch.linspace(-1.0, 2.0, heads).cuda()
+        r1, r2 = (torch.rand(heads) * 0.2).cuda(), (torch.rand(heads) * 0.5 + 0.01).cuda()
+        for kind in ("plain", "penalty", "sink", "sink_cross"):
+            extra = {"penalty": dict(r1=r1, r2=r2), "sink": dict(sink=sink), "sink_cross": dict(sink=sink, cross=True)}.get(kind, {})
+            slots = groups if kind == "sink_cross" else 1
+            want = torch.empty(total, heads, slots, size, dtype=torch.float32, device="cuda")
+            got = torch.full((total, heads, slots, size), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.attention_scored(q.cuda(), k_cache, v_cache, want, table.cuda(), seg, pos, 0.3, tensor_cores=False, **extra)
+            ops.attention_scored_tc(q.cuda(), k_cache, v_cache, got, table.cuda(), starts, first_pos, 0.3, **extra)
+            assert ops.attention_tc_status() == 0
+            error = float((got.float() - want).abs().max())
+            assert error <= 2e-2 * max(1.0, float(want.abs().max())), (heads, groups, size, kind, error)
+
+
+def test_long_prompts_take_the_tcgen05_kernel_and_agree_with_the_plain_model():
+    """Heads of 64 and 128: prompts of 128 rows and more run on the tcgen05 kernel in bfloat16 (whole, and in portions
+    behind a prefix), shorter steps on the mma.sync kernel; the logits agree with the plain model either way."""
+    from llm_serving_engine_b200.models import load_model
+
+    name = "tensor_core_sizes"
+    CONFIGS[name] = model([attention2(heads=4, kv_heads=2, dim=64, vdim=64), attention(heads=2, kv_heads=1, dim=128, vdim=128),
+                           attention(heads=4, kv_heads=1, dim=128, vdim=128, kv_from=1, mlp=None),
+                           attention2(heads=2, kv_heads=2, dim=128, vdim=128, mlp=None)], width=96, positions=700)
+    engine_model = load_model(folder_of(name), dtype="bfloat16")
+    assert engine_model.launch_signature([300]) == (("tcgen05",),) and engine_model.launch_signature([100, 20]) == ()
+    requests = some_requests(name, [330, 140], seed=13)
+    got = replay(name, "bfloat16", helpers.trace_whole(requests), helpers.max_tokens_for(requests))
+    compare(name, "bfloat16", requests, got, "whole prompts on tcgen05")
+    got = replay(name, "bfloat16", helpers.trace_portions(requests, (150, 130, 20, 2)), helpers.max_tokens_for(requests))
+    compare(name, "bfloat16", requests, got, "portions on tcgen05")
