@@ -452,7 +452,7 @@ def test_mixture_of_experts_against_the_plain_mixture(rows):
     expert, more chosen than real experts, odd sizes."""
     for case, (experts, identity, top, ff, limit, shared, width) in enumerate((
             (5, 2, 3, 40, 0.8, (56, 1.5), 72), (4, 0, 1, 24, 0.5, None, 64), (1, 3, 3, 18, 0.3, (10, 0.5), 102),
-            (12, 4, 3, 64, 1.0, (96, 2.0), 128))):
+            (10, 3, 4, 48, 1.2, (80, 1.8), 128))):
         got, want, *_ = _mixture_case(experts, identity, top, ff, limit, shared, width, rows, seed=10 * rows + case)
         assert float((got - want).abs().max()) <= 3e-5 * float(want.abs().max()), (rows, case)
 
@@ -490,7 +490,7 @@ def test_tensor_core_attention_against_the_general_kernel():
 
     torch.manual_seed(8)
     page = 16
-    for heads, groups, size in ((4, 2, 48), (3, 1, 32), (8, 8, 64), (16, 2, 128), (18, 2, 96), (4, 2, 64)):
+    for heads, groups, size in ((6, 3, 48), (3, 1, 32), (8, 8, 64), (16, 2, 128), (18, 2, 96), (6, 2, 64)):
         counts, firsts = [70, 1, 33, 1, 5], [300, 519, 0, 0, 63]
         contexts = [first + count for first, count in zip(firsts, counts)]
         pages_each = [-(-context // page) for context in contexts]
@@ -538,7 +538,7 @@ def test_mixture_of_experts_in_bfloat16_both_ways_through_the_experts(rows, monk
 
     for case, (experts, identity, top, ff, limit, shared, width) in enumerate((
             (5, 2, 3, 40, 0.8, (56, 1.5), 72), (4, 0, 1, 24, 0.5, None, 64), (2, 6, 2, 16, 0.3, (8, 0.5), 104),
-            (12, 4, 3, 64, 1.0, (96, 2.0), 128))):
+            (10, 3, 4, 48, 1.2, (80, 1.8), 128))):
         got, want, *_ = _mixture_case(experts, identity, top, ff, limit, shared, width, rows, seed=10 * rows + case,
                                       dtype=torch.bfloat16)
         scale = float(want.abs().max())
@@ -583,7 +583,7 @@ def test_tcgen05_attention_against_the_general_kernel():
 
     torch.manual_seed(11)
     page = 16
-    for heads, groups, size in ((4, 2, 64), (8, 1, 128), (3, 3, 128)):
+    for heads, groups, size in ((6, 2, 64), (8, 1, 128), (3, 3, 128)):
         counts, firsts = [300, 1, 129, 140], [0, 77, 500, 1000]
         contexts = [first + count for first, count in zip(firsts, counts)]
         pages_each = [-(-context // page) for context in contexts]
@@ -623,7 +623,7 @@ def test_long_prompts_take_the_tcgen05_kernel_and_agree_with_the_plain_model():
     from llm_serving_engine_b200.models import load_model
 
     name = "tensor_core_sizes"
-    CONFIGS[name] = model([attention2(heads=4, kv_heads=2, dim=64, vdim=64), attention(heads=2, kv_heads=1, dim=128, vdim=128),
+    CONFIGS[name] = model([attention2(heads=6, kv_heads=3, dim=64, vdim=64), attention(heads=2, kv_heads=1, dim=128, vdim=128),
                            attention(heads=4, kv_heads=1, dim=128, vdim=128, kv_from=1, mlp=None),
                            attention2(heads=2, kv_heads=2, dim=128, vdim=128, mlp=None)], width=96, positions=700)
     engine_model = load_model(folder_of(name), dtype="bfloat16")
